@@ -20,7 +20,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..parts.base import FixedState, PagedKV
+from ..parts.base import CacheParts, FixedState, PagedKV  # noqa: F401  (CacheParts: part of this module's interface)
 
 
 @dataclass
@@ -28,13 +28,15 @@ class LayerCache:
     """What a layer's mixer gets: its group (index into the step context's
     groups, -1 for none), whether it writes, and its storage: `k_pool`/`v_pool`
     for keys and values, `state` for a slot kind, `pages` for a paged kind with a
-    layout of its own."""
+    layout of its own.  A mixer made of several (its need was a `CacheParts`) gets
+    its members' caches in `parts`."""
     group: int = -1
     writes: bool = True
     k_pool: Optional[torch.Tensor] = None
     v_pool: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None
     pages: Optional[torch.Tensor] = None
+    parts: Optional[list] = None
 
 
 class CacheKind:
@@ -43,6 +45,10 @@ class CacheKind:
     # -- kinds kept in pages ---------------------------------------------------
     def window(self, spec) -> int:
         """Positions a query still reads (0: all).  Pages behind it are given back."""
+        return 0
+
+    def keep_first(self, spec) -> int:
+        """With a window: the first positions that stay readable all the same."""
         return 0
 
     def page_bytes(self, spec, page_size: int, element_bytes: int) -> int:
@@ -57,6 +63,11 @@ class CacheKind:
         """What layer `index` of the group's storage hands its mixer."""
         raise NotImplementedError
 
+    def layer_cache_of(self, spec, storage: Optional[torch.Tensor], index: int, group: int,
+                       page_size: int) -> LayerCache:
+        """The same for kinds whose layout depends on the spec (the manager calls this one)."""
+        return self.layer_cache(storage, index, group)
+
     # -- kinds kept in slots ---------------------------------------------------
     def allocate_state(self, spec, slots: int, device) -> torch.Tensor:
         raise NotImplementedError
@@ -68,21 +79,38 @@ class CacheKind:
 class PagedKVKind(CacheKind):
     """Keys and values of every position: [layer, K|V, page, kv head, offset in page,
     head_dim] (the reference keeps a K and a V pool [page, kv head, offset, head_dim]
-    per layer, src/paged/pages.rs:62-74, 101-109)."""
+    per layer, src/paged/pages.rs:62-74, 101-109).  Where a value has another size
+    than a key, a layer's storage is flat: its K pool [page, kv head, offset, head_dim]
+    followed by its V pool [page, kv head, offset, v_head_dim]."""
 
     def window(self, spec: PagedKV) -> int:
         return spec.window
 
+    def keep_first(self, spec: PagedKV) -> int:
+        return spec.keep_first if spec.window > 0 else 0
+
     def page_bytes(self, spec: PagedKV, page_size, element_bytes):
-        return 2 * spec.num_kv_heads * spec.head_dim * page_size * element_bytes
+        return spec.num_kv_heads * (spec.head_dim + spec.value_dim) * page_size * element_bytes
 
     def allocate(self, spec: PagedKV, layers, num_pages, page_size, dtype, device):
-        return torch.empty((layers, 2, num_pages, spec.num_kv_heads, page_size, spec.head_dim), dtype=dtype, device=device)
+        if spec.value_dim == spec.head_dim:
+            return torch.empty((layers, 2, num_pages, spec.num_kv_heads, page_size, spec.head_dim), dtype=dtype, device=device)
+        cells = num_pages * spec.num_kv_heads * page_size
+        return torch.empty((layers, cells * (spec.head_dim + spec.value_dim)), dtype=dtype, device=device)
 
     def layer_cache(self, storage, index, group):
         if storage is None:
             return LayerCache(group, True)
         return LayerCache(group, True, storage[index, 0], storage[index, 1], None, storage[index])
+
+    def layer_cache_of(self, spec: PagedKV, storage, index, group, page_size):
+        if storage is None or storage.dim() != 2:
+            return self.layer_cache(storage, index, group)
+        cells = storage.shape[1] // (spec.head_dim + spec.value_dim)   # pages * kv heads * page size
+        flat = storage[index]
+        k = flat[:cells * spec.head_dim].view(-1, spec.num_kv_heads, page_size, spec.head_dim)
+        v = flat[cells * spec.head_dim:].view(-1, spec.num_kv_heads, page_size, spec.value_dim)
+        return LayerCache(group, True, k, v, None, flat)
 
 
 class FixedStateKind(CacheKind):

@@ -36,7 +36,7 @@ import torch
 
 from .. import native
 from ..native import OutOfPages  # noqa: F401  (part of this module's interface)
-from .kinds import CacheKind, LayerCache, cache_kind
+from .kinds import CacheKind, CacheParts, LayerCache, cache_kind
 from .pages import CacheAccountingError, PageAllocator, SlotAllocator
 
 
@@ -99,20 +99,28 @@ class CacheManager:
         self.groups: List[CacheGroup] = []
         self._layers: List[LayerCache] = []
         self._state_layers: List[int] = []
+        # A place whose mixer is made of several (`CacheParts`) has one cell per member;
+        # every other place has one cell.  Cells are what groups and state tensors are made of.
+        cells: List[object] = []
+        cells_of_place: List[List[int]] = []
+        for spec in cache_specs:
+            members = list(spec.parts) if isinstance(spec, CacheParts) else [spec]
+            cells_of_place.append(list(range(len(cells), len(cells) + len(members))))
+            cells.extend(members)
         by_spec: Dict[object, int] = {}
-        n_layers = len(cache_specs)
-        layer_group = [-1] * n_layers
+        cell_group = [-1] * len(cells)
         specs_of_groups: List[object] = []
-        layers_of_groups: List[List[int]] = []
-        kinds = [None if spec is None else cache_kind(spec) for spec in cache_specs]
-        for i, spec in enumerate(cache_specs):
-            if spec is not None and kinds[i].paged:
+        cells_of_groups: List[List[int]] = []
+        kinds = [None if spec is None else cache_kind(spec) for spec in cells]
+        for c, spec in enumerate(cells):
+            if spec is not None and kinds[c].paged:
                 if spec not in by_spec:
                     by_spec[spec] = len(specs_of_groups)
                     specs_of_groups.append(spec)
-                    layers_of_groups.append([])
-                layer_group[i] = by_spec[spec]
-                layers_of_groups[by_spec[spec]].append(i)
+                    cells_of_groups.append([])
+                cell_group[c] = by_spec[spec]
+                cells_of_groups[by_spec[spec]].append(c)
+        place_of_cell = {c: i for i, cs in enumerate(cells_of_place) for c in cs}
         # the books: pools, block tables, slots and lengths live in the host library
         self._lib = native.library()
         if num_pages <= 0:
@@ -122,9 +130,13 @@ class CacheManager:
                                                                 int(num_pages), int(max_requests), self.max_blocks))
         if not self._book:
             raise ValueError("page size, pages, requests and blocks per request must be positive")
+        for g, spec in enumerate(specs_of_groups):
+            kept = int(cache_kind(spec).keep_first(spec))
+            if kept:
+                native.check(self._lib.vxh_cache_set_keep_first(self._book, g, kept))
         self.slots = SlotAllocator(0, _borrowed=self._lib.vxh_cache_slots(self._book), _owner=self)
-        for g, (spec, layers) in enumerate(zip(specs_of_groups, layers_of_groups)):
-            self.groups.append(CacheGroup(spec, cache_kind(spec), layers,
+        for g, (spec, members) in enumerate(zip(specs_of_groups, cells_of_groups)):
+            self.groups.append(CacheGroup(spec, cache_kind(spec), sorted({place_of_cell[c] for c in members}),
                                           PageAllocator(0, _borrowed=self._lib.vxh_cache_pool(self._book, g), _owner=self)))
         # request ids: non-negative integers are their own handle in the library
         # (the scheduler's ids are such), anything else gets a negative one
@@ -132,29 +144,41 @@ class CacheManager:
         self._names: Dict[int, object] = {}
         self._next_handle = -1
         self.requests = _Requests(self)
-        for g in self.groups:
+        for g, members in zip(self.groups, cells_of_groups):
             if device is not None:
-                g.storage = g.kind.allocate(g.spec, len(g.layers), num_pages, self.page_size, dtype, device)
+                g.storage = g.kind.allocate(g.spec, len(members), num_pages, self.page_size, dtype, device)
                 if poison and g.storage.is_floating_point():
                     g.storage.fill_(float("nan"))
                 else:
                     g.storage.zero_()
-        self._state_kinds: Dict[int, CacheKind] = {}
-        for i, spec in enumerate(cache_specs):
+        # state tensors, with the kind that clears a slot of each
+        self._states: List = []
+        cell_cache: List[LayerCache] = []
+        for c, spec in enumerate(cells):
             if spec is None:
-                self._layers.append(LayerCache())
-            elif kinds[i].paged:
-                g = self.groups[layer_group[i]]
-                self._layers.append(g.kind.layer_cache(g.storage, g.layers.index(i), layer_group[i]))
+                cell_cache.append(LayerCache())
+            elif kinds[c].paged:
+                g = self.groups[cell_group[c]]
+                cell_cache.append(g.kind.layer_cache_of(g.spec, g.storage, cells_of_groups[cell_group[c]].index(c),
+                                                        cell_group[c], self.page_size))
             else:
-                st = kinds[i].allocate_state(spec, max_requests, device) if device is not None else None
-                self._layers.append(LayerCache(-1, True, None, None, st))
-                self._state_layers.append(i)
-                self._state_kinds[i] = kinds[i]
+                st = kinds[c].allocate_state(spec, max_requests, device) if device is not None else None
+                cell_cache.append(LayerCache(-1, True, None, None, st))
+                self._states.append((kinds[c], st))
+                if place_of_cell[c] not in self._state_layers:
+                    self._state_layers.append(place_of_cell[c])
+        for i, spec in enumerate(cache_specs):
+            mine = [cell_cache[c] for c in cells_of_place[i]]
+            self._layers.append(LayerCache(parts=mine) if isinstance(spec, CacheParts) else mine[0])
         for i, j in enumerate(cache_of):
             if j is not None:
-                src = self._layers[j]
-                self._layers[i] = LayerCache(src.group, False, src.k_pool, src.v_pool, src.state, src.pages)
+                self._layers[i] = self._reader(self._layers[j])
+
+    @classmethod
+    def _reader(cls, src: LayerCache) -> LayerCache:
+        """The cache of a place that reads (and does not write) another place's."""
+        return LayerCache(src.group, False, src.k_pool, src.v_pool, src.state, src.pages,
+                          None if src.parts is None else [cls._reader(p) for p in src.parts])
 
     def __del__(self):
         book = getattr(self, "_book", None)
@@ -183,10 +207,9 @@ class CacheManager:
         return native.int64_array(self._known(r) for r in request_ids)
 
     def zero_state(self, slot: int) -> None:
-        for i in self._state_layers:
-            st = self._layers[i].state
+        for kind, st in self._states:
             if st is not None:
-                self._state_kinds[i].clear_slot(st, slot)
+                kind.clear_slot(st, slot)
 
     # -- what layers see -------------------------------------------------------
     def layer(self, i: int) -> LayerCache:

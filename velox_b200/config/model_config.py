@@ -168,3 +168,126 @@ class Qwen3Config(ModelConfig):
         if not self.use_sliding_window or not self.sliding_window:
             return 0
         return int(self.sliding_window) if layer >= self.max_window_layers else 0
+
+
+@dataclass(frozen=True)
+class DobepelConfig(ModelConfig):
+    """Dobepel: a decoder whose config.json is nested and lists its layers one by one.
+
+        architecture   "Dobepel"
+        vocab, width, residual_mult, norm.eps
+        embedding.bigram   buckets, mul_prev, mul_cur
+        layers[i]      type ("parallel"), mixer.left (heads, kv_heads, dim, vdim, scale, mask.size,
+                       mask.keep_first), mixer.right (heads, dim, vdim, decay per head),
+                       mlp: null | kind "dense" (ff) | kind "moe" (expert.ff, router.experts,
+                       router.top, shared.ff or no shared)
+
+    Every size and constant is read from there; the layers may differ from one another."""
+
+    architecture: ClassVar[str] = "Dobepel"
+    model_type: ClassVar[str] = "dobepel"
+    LAYER_TYPES: ClassVar[Tuple[str, ...]] = ("parallel",)
+
+    vocab: int = _field(int)
+    width: int = _field(int)
+    residual_mult: float = _field(float)
+    norm_eps: float = _field(float)
+    bigram_buckets: int = _field(int)
+    bigram_mul_prev: int = _field(int)
+    bigram_mul_cur: int = _field(int)
+    layers: Tuple[Dict[str, Any], ...] = _field(tuple, default=())
+
+    @classmethod
+    def from_dict(cls, raw: Dict[str, Any]) -> "DobepelConfig":
+        faults: list = []
+
+        def get(d, path, kind, default=dataclasses.MISSING):
+            cur = d
+            for key in path.split("."):
+                if not isinstance(cur, dict) or cur.get(key) is None:
+                    if default is dataclasses.MISSING:
+                        faults.append("missing key %r" % path)
+                    return None if default is dataclasses.MISSING else default
+                cur = cur[key]
+            return _typed(path, cur, kind, faults)
+
+        values = dict(vocab=get(raw, "vocab", int), width=get(raw, "width", int),
+                      residual_mult=get(raw, "residual_mult", float, 1.0), norm_eps=get(raw, "norm.eps", float),
+                      bigram_buckets=get(raw, "embedding.bigram.buckets", int),
+                      bigram_mul_prev=get(raw, "embedding.bigram.mul_prev", int),
+                      bigram_mul_cur=get(raw, "embedding.bigram.mul_cur", int))
+        layers = raw.get("layers")
+        if not isinstance(layers, list) or not layers:
+            faults.append("key 'layers': expected a list of layers")
+            layers = []
+        if faults:
+            raise ConfigError("config.json for %s: %s" % (cls.__name__, "; ".join(faults)))
+        cfg = cls(layers=tuple(json.loads(json.dumps(layer)) for layer in layers), **values)
+        cfg.validate()
+        return cfg
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"architecture": self.architecture,
+                "embedding": {"bigram": {"buckets": self.bigram_buckets, "mul_prev": self.bigram_mul_prev,
+                                         "mul_cur": self.bigram_mul_cur}},
+                "layers": json.loads(json.dumps(list(self.layers))), "norm": {"eps": self.norm_eps},
+                "residual_mult": self.residual_mult, "vocab": self.vocab, "width": self.width}
+
+    def validate(self) -> None:
+        faults = []
+
+        def positive(where, d, *keys):
+            for k in keys:
+                v = d.get(k) if isinstance(d, dict) else None
+                if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+                    faults.append("%s.%s must be a positive integer, got %r" % (where, k, v))
+                    return False
+            return True
+
+        for name in ("vocab", "width", "bigram_buckets"):
+            if getattr(self, name) <= 0:
+                faults.append("%s must be positive, got %d" % (name, getattr(self, name)))
+        if self.bigram_mul_prev < 0 or self.bigram_mul_cur < 0:
+            faults.append("the bigram multipliers must not be negative")
+        if not self.norm_eps > 0:
+            faults.append("norm.eps must be positive, got %r" % self.norm_eps)
+        for i, layer in enumerate(self.layers):
+            at = "layers[%d]" % i
+            if not isinstance(layer, dict) or layer.get("type") not in self.LAYER_TYPES:
+                faults.append("%s.type %r is not one of %s" % (at, layer.get("type") if isinstance(layer, dict) else layer,
+                                                               list(self.LAYER_TYPES)))
+                continue
+            mixer = layer.get("mixer") or {}
+            left, right = mixer.get("left"), mixer.get("right")
+            if positive(at + ".mixer.left", left, "heads", "kv_heads", "dim", "vdim"):
+                if left["heads"] % left["kv_heads"]:
+                    faults.append("%s.mixer.left: heads (%d) is not a multiple of kv_heads (%d)"
+                                  % (at, left["heads"], left["kv_heads"]))
+                if not isinstance(left.get("scale"), (int, float)) or isinstance(left.get("scale"), bool):
+                    faults.append("%s.mixer.left.scale must be a number, got %r" % (at, left.get("scale")))
+                mask = left.get("mask") or {}
+                for k in ("size", "keep_first"):
+                    v = mask.get(k, 0)
+                    if not isinstance(v, int) or isinstance(v, bool) or v < 0:
+                        faults.append("%s.mixer.left.mask.%s must be an integer >= 0, got %r" % (at, k, v))
+            if positive(at + ".mixer.right", right, "heads", "dim", "vdim"):
+                decay = right.get("decay")
+                if not isinstance(decay, list) or len(decay) != right["heads"] or \
+                        not all(isinstance(d, (int, float)) and not isinstance(d, bool) for d in decay):
+                    faults.append("%s.mixer.right.decay must list one number per head" % at)
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if not isinstance(mlp, dict) or mlp.get("kind") not in ("dense", "moe"):
+                faults.append("%s.mlp.kind %r is not one of ['dense', 'moe']" % (at, mlp.get("kind") if isinstance(mlp, dict) else mlp))
+            elif mlp["kind"] == "dense":
+                positive(at + ".mlp", mlp, "ff")
+            else:
+                positive(at + ".mlp.expert", mlp.get("expert"), "ff")
+                if positive(at + ".mlp.router", mlp.get("router"), "experts", "top") and \
+                        mlp["router"]["top"] > mlp["router"]["experts"]:
+                    faults.append("%s.mlp.router: top (%d) exceeds experts (%d)" % (at, mlp["router"]["top"], mlp["router"]["experts"]))
+                if mlp.get("shared") is not None:
+                    positive(at + ".mlp.shared", mlp["shared"], "ff")
+        if faults:
+            raise ConfigError("Dobepel configuration: " + "; ".join(faults))

@@ -59,6 +59,8 @@ def resolve_architecture(raw: Dict[str, Any]) -> Architecture:
     names = raw.get("architectures") or []
     if isinstance(names, str):
         names = [names]
+    if isinstance(raw.get("architecture"), str):   # (some configurations name one architecture, in the singular)
+        names = list(names) + [raw["architecture"]]
     for n in names:
         if n in _BY_NAME:
             return _BY_NAME[n]

@@ -1,12 +1,16 @@
-// Paged causal attention, the general kernel: any head size up to 256, any
-// number of heads and groups, any page size, an optional
-// window, element type float or bfloat16.  It serves prompt portions and decoded
+// Paged causal attention, the general kernel: any head size up to 256 (values may
+// have another size than keys), any number of heads and groups, any page size, an
+// optional window with optionally kept first positions, an optional bias by distance,
+// element type float or bfloat16.  It serves prompt portions and decoded
 // tokens alike, and it is the whole of the 32-bit path.
 //
 // One block per (token, query head).  The token's absolute position p gives its
-// keys: j in [start, p], start = max(0, p + 1 - window) with a window, else 0.
+// keys: j in [start, p], start = max(0, p + 1 - window) with a window, else 0; with
+// keep_first > 0 also j in [0, min(keep_first, start)), at their true positions.
 // Key j of the token's request lies in page block_table[seq, j / S] at offset
-// j % S; pools are [page, Hk, S, D]; query head h reads kv head h / (H / Hk).
+// j % S; pools are [page, Hk, S, D] and [page, Hk, S, Dv]; query head h reads kv head
+// h / (H / Hk).  score = q.k * scale - slope_h * (p - j) with
+// slope_h = 2^(-bias_exp * (h + 1) / H), or no bias for bias_exp = 0.
 //
 // Each warp takes chunks of 32 keys (chunk c goes to warp c mod 4), one key per
 // lane: the lane forms the whole dot product q.k in float32, the warp keeps a
@@ -25,7 +29,8 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ q, int q_row_stride, const T* __restrict__ k_pool,
     const T* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, T* __restrict__ out,
-    int out_row_stride, float scale, int window, int H, int Hk, int D, int S) {
+    int out_row_stride, float scale, int window, int H, int Hk, int D, int S, int Dv, int keep_first,
+    float bias_exp) {
     pdl_wait();
     pdl_trigger();
     __shared__ float q_s[ATT_MAX_D];
@@ -38,6 +43,8 @@ __global__ void paged_attention_generic_kernel(
     const int seq = seq_of_token[t];
     const int kv_len = positions[t] + 1;
     const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    const int nkept = min(keep_first, start);   // kept first positions that lie before the window
+    const float slope = bias_exp > 0.f ? exp2f(-bias_exp * (float)(h + 1) / (float)H) : 0.f;
     const int* bt = block_table + (size_t)seq * max_blocks;
 
     for (int d = threadIdx.x; d < D; d += blockDim.x)
@@ -50,20 +57,21 @@ __global__ void paged_attention_generic_kernel(
     for (int i = 0; i < NR; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
 
-    const int nkeys = kv_len - start;
+    const int nkeys = nkept + kv_len - start;   // the n-th visible key is j = n (kept) or start + n - nkept
     const int nchunks = (nkeys + 31) >> 5;
     for (int c = warp; c < nchunks; c += ATT_WARPS) {
-        const int j = start + c * 32 + lane;
-        const bool valid = j < kv_len;
+        const int n = c * 32 + lane;
+        const int j = n < nkept ? n : start + n - nkept;
+        const bool valid = n < nkeys;
         size_t base = 0;
         float s = -INFINITY;
         if (valid) {
             const int page = bt[j / S];
-            base = (((size_t)page * Hk + hk) * S + (j % S)) * D;
-            const T* kp = k_pool + base;
+            base = ((size_t)page * Hk + hk) * S + (j % S);
+            const T* kp = k_pool + base * D;
             float dot = 0.f;
             for (int d = 0; d < D; ++d) dot += q_s[d] * to_f32(kp[d]);
-            s = dot * scale;
+            s = dot * scale - slope * (float)(kv_len - 1 - j);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -71,15 +79,15 @@ __global__ void paged_attention_generic_kernel(
         l = l * alpha + warp_sum(p);
 #pragma unroll
         for (int i = 0; i < NR; ++i) acc[i] *= alpha;
-        const int nvalid = min(32, kv_len - (start + c * 32));
+        const int nvalid = min(32, nkeys - c * 32);
         for (int jj = 0; jj < nvalid; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const size_t bj = __shfl_sync(0xffffffffu, (unsigned long long)base, jj);
-            const T* vp = v_pool + bj;
+            const T* vp = v_pool + bj * Dv;
 #pragma unroll
             for (int i = 0; i < NR; ++i) {
                 const int d = lane + 32 * i;
-                if (d < D) acc[i] += pj * to_f32(vp[d]);
+                if (d < Dv) acc[i] += pj * to_f32(vp[d]);
             }
         }
         m = m_new;
@@ -89,7 +97,7 @@ __global__ void paged_attention_generic_kernel(
 #pragma unroll
     for (int i = 0; i < NR; ++i) {
         const int d = lane + 32 * i;
-        if (d < D) acc_s[warp][d] = acc[i];
+        if (d < Dv) acc_s[warp][d] = acc[i];
     }
     __syncthreads();
     float M = -INFINITY;
@@ -100,10 +108,10 @@ __global__ void paged_attention_generic_kernel(
         wgt[w] = (m_s[w] == -INFINITY) ? 0.f : expf(m_s[w] - M);
         L += l_s[w] * wgt[w];
     }
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < ATT_WARPS; ++w) o += acc_s[w][d] * wgt[w];
-        out[(size_t)t * out_row_stride + (size_t)h * D + d] = from_f32<T>(o / L);
+        out[(size_t)t * out_row_stride + (size_t)h * Dv + d] = from_f32<T>(o / L);
     }
 }
 
@@ -111,18 +119,20 @@ extern "C" int vx_paged_attention_generic(const void* q, int q_row_stride, const
                                           const void* v_pool, const int* block_table, int max_blocks,
                                           const int* seq_of_token, const int* positions, void* out,
                                           int out_row_stride, float scale, int window, int tokens,
-                                          int H, int Hk, int D, int S, int dtype, cudaStream_t stream) {
+                                          int H, int Hk, int D, int S, int dtype, int Dv, int keep_first,
+                                          float bias_exp, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
-    if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > ATT_MAX_D || S <= 0 || max_blocks <= 0)
+    if (Dv <= 0) Dv = D;
+    if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > ATT_MAX_D || Dv > ATT_MAX_D || S <= 0 || max_blocks <= 0)
         return VX_ERR_SHAPE;
-    if (window < 0) return VX_ERR_SHAPE;
+    if (window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
     dim3 grid(tokens, H);
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<float>), grid, ATT_WARPS * 32, 0, stream, (const float*)q, q_row_stride, (const float*)k_pool, (const float*)v_pool, block_table,
-            max_blocks, seq_of_token, positions, (float*)out, out_row_stride, scale, window, H, Hk, D, S);
+            max_blocks, seq_of_token, positions, (float*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp);
     else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<bf16>), grid, ATT_WARPS * 32, 0, stream, (const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-            max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, scale, window, H, Hk, D, S);
+            max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

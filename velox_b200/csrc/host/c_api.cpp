@@ -42,6 +42,13 @@ void* vxh_cache_create(int n_groups, const int* windows, int page_size, int num_
     return new CacheBook(n_groups, windows, page_size, num_pages, max_requests, max_blocks);
 }
 void vxh_cache_destroy(void* c) { delete (CacheBook*)c; }
+// the first positions that a group with a window never gives back
+int vxh_cache_set_keep_first(void* c, int g, int n) {
+    CacheBook* b = (CacheBook*)c;
+    if (g < 0 || g >= b->num_groups() || n < 0) return fail(ERR_VALUE, "keep_first: no such group, or a negative count");
+    b->group(g).keep_first = n;
+    return OK;
+}
 void* vxh_cache_pool(void* c, int g) { return &((CacheBook*)c)->group(g).pool; }
 void* vxh_cache_slots(void* c) { return &((CacheBook*)c)->slots(); }
 int vxh_cache_add(void* c, int64_t rid) { return ((CacheBook*)c)->add(rid); }

@@ -6,8 +6,8 @@
 // step needs them (reserve), not for the worst case at admission as the
 // reference does (src/paged/scheduler.rs:255).  They are given back when the
 // request ends, and in a group with a window as soon as every position of a page
-// lies before the window of the next query; the freed page is the next one
-// handed out.  Beside the tables the book keeps, per group, a dense mirror
+// lies before the window of the next query (pages that hold one of the group's kept
+// first positions stay); the freed page is the next one handed out.  Beside the tables the book keeps, per group, a dense mirror
 // [slot, block] (-1 where no page is held), from which the step builders copy
 // whole rows.
 //
@@ -32,6 +32,7 @@ struct RequestCache {
 
 struct CacheGroup {
     int window;
+    int keep_first = 0;  // with a window: the first positions that every later query still reads
     PagePool pool;
     std::vector<int32_t> mirror;  // [max_requests, max_blocks]
     CacheGroup(int window_, int num_pages, size_t cells) : window(window_), pool(num_pages), mirror(cells, -1) {}
@@ -129,7 +130,8 @@ public:
                 // the first page that the query at position `length` can still see
                 const int64_t first_key = std::max<int64_t>(0, rc->length + 1 - groups_[g].window);
                 const int64_t keep_from = std::min<int64_t>(first_key / page_size_, (int64_t)table.size());
-                for (int64_t i = 0; i < keep_from; ++i) {
+                const int64_t kept_pages = ((int64_t)groups_[g].keep_first + page_size_ - 1) / page_size_;
+                for (int64_t i = kept_pages; i < keep_from; ++i) {
                     if (table[i] < 0) continue;
                     if (int e = groups_[g].pool.free(&table[i], 1)) return e;
                     table[i] = -1;

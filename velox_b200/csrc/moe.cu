@@ -1,0 +1,387 @@
+// A routed feed-forward (mixture of experts) without a trip to the host:
+//
+//   route     per token: logits = W_r h + b in float32, the `top` largest (lowest index first
+//             among equals), softmax over the chosen logits only; counts the tokens of every expert
+//   plan      one block: where each expert's rows start in expert order, the list of row tiles
+//             (expert, first row, rows) that the grouped products walk, and for every
+//             assignment (token, k) its row in expert order
+//   grouped product   C[p, :] = A[src(p), :] W_e^T for the rows p of each tile, W = [experts, N, K];
+//             optionally with act(gate) * up on the accumulators (W's rows in tiles of 8 gate rows
+//             followed by their 8 up rows)
+//   combine   out[t] = sum_k weight[t, k] * y[row of (t, k)] (+ shared[t]) in float32, k ascending
+//
+// The grid of a grouped product is sized for the worst case (assignments / tile rows + experts
+// tiles); blocks beyond the step's real number of tiles leave at once.  Which tile a row falls
+// into depends on the batch, but a row's sums run over k in ascending order whatever its tile, so
+// a token's result does not depend on what else is in the step.
+#include "mma_helpers.cuh"
+
+#define MOE_MAX_EXPERTS 256
+#define MOE_MAX_TOP 32
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_router, const float* __restrict__ bias,
+                 int tokens, int K, int E, int top, int* __restrict__ chosen, float* __restrict__ weight,
+                 int* __restrict__ counts, int* __restrict__ pos) {
+    __shared__ float z_s[4][MOE_MAX_EXPERTS];
+    __shared__ float zc_s[4][MOE_MAX_TOP];
+    pdl_wait();
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= tokens) return;
+    const T* row = h + (size_t)t * ldh;
+    float* z = z_s[warp];
+    for (int e = 0; e < E; ++e) {
+        const float* w = w_router + (size_t)e * K;
+        float s = 0.f;
+        for (int k = lane; k < K; k += 32) s = fmaf(to_f32(row[k]), w[k], s);
+        s = warp_sum(s);
+        if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    for (int i = 0; i < top; ++i) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < arg)) { best = v; arg = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (lane == 0) {
+            zc_s[warp][i] = best;
+            z[arg] = -INFINITY;
+            chosen[(size_t)t * top + i] = arg;
+            pos[(size_t)t * top + i] = atomicAdd(&counts[arg], 1);
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float m = zc_s[warp][0];
+        float sum = 0.f;
+        for (int i = 0; i < top; ++i) sum += expf(zc_s[warp][i] - m);
+        for (int i = 0; i < top; ++i) weight[(size_t)t * top + i] = expf(zc_s[warp][i] - m) / sum;
+    }
+}
+
+// tiles: int3 per tile (expert, first row in expert order, rows); n_tiles[0] their number.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ chosen, const int* __restrict__ pos, int* __restrict__ counts, int assignments,
+                int E, int tile_rows, int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ n_tiles,
+                int* __restrict__ src_of_row, int* __restrict__ row_of) {
+    __shared__ int off_s[MOE_MAX_EXPERTS + 1];
+    pdl_wait();
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        int run = 0, n = 0;
+        for (int e = 0; e < E; ++e) {
+            off_s[e] = run;
+            offsets[e] = run;
+            const int c = counts[e];
+            for (int r = 0; r < c; r += tile_rows) {
+                tiles[3 * n] = e;
+                tiles[3 * n + 1] = run + r;
+                tiles[3 * n + 2] = min(tile_rows, c - r);
+                ++n;
+            }
+            run += c;
+        }
+        off_s[E] = run;
+        offsets[E] = run;
+        n_tiles[0] = n;
+    }
+    __syncthreads();
+    for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
+        const int p = off_s[chosen[a]] + pos[a];
+        src_of_row[p] = a;
+        row_of[a] = p;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;   // ready for the next step
+}
+
+extern "C" int vx_moe_route(const void* h, int ldh, const float* w_router, const float* bias, int tokens, int K, int E,
+                            int top, int tile_rows, int* chosen, float* weight, int* counts, int* pos, int* offsets,
+                            int* tiles, int* n_tiles, int* src_of_row, int* row_of, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VX_OK;
+    if (K <= 0 || E <= 0 || top <= 0 || top > E || tile_rows <= 0) return VX_ERR_SHAPE;
+    if (E > MOE_MAX_EXPERTS || top > MOE_MAX_TOP) return VX_ERR_LIMIT;
+    const int blocks = (tokens + 3) / 4;
+    if (dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_route_kernel<float>), blocks, 128, 0, stream, (const float*)h, ldh, w_router, bias,
+                    tokens, K, E, top, chosen, weight, counts, pos);
+    else if (dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_route_kernel<bf16>), blocks, 128, 0, stream, (const bf16*)h, ldh, w_router, bias,
+                    tokens, K, E, top, chosen, weight, counts, pos);
+    else
+        return VX_ERR_DTYPE;
+    VX_LAUNCH_K(VX_K_ELEMENTWISE, moe_plan_kernel, 1, 1024, 0, stream, (const int*)chosen, (const int*)pos, counts,
+                tokens * top, E, tile_rows, offsets, tiles, n_tiles, src_of_row, row_of);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// ---- grouped product on the CUDA cores: any sizes, float32 sums over k ascending ----
+#define MG_BM 64
+#define MG_BN 64
+#define MG_BK 16
+
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(256)
+moe_gemm_simt_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ src_of_row, int src_div,
+                     const TA* __restrict__ W, const int* __restrict__ tiles, const int* __restrict__ n_tiles,
+                     TC* __restrict__ C, int ldc, int N, int K, int gated, int act) {
+    pdl_wait();
+    pdl_trigger();
+    if ((int)blockIdx.y >= n_tiles[0]) return;
+    __shared__ float As[MG_BK][MG_BM + 1];
+    __shared__ float Ws[MG_BK][MG_BN + 1];
+    __shared__ int src_s[MG_BM];
+    const int e = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    const TA* We = W + (size_t)e * N * K;
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int n0 = blockIdx.x * MG_BN;
+    const int lk = tid & 15, lr = tid >> 4;
+    if (tid < MG_BM) {
+        const int p = row0 + tid;
+        src_s[tid] = tid < rows ? (src_of_row ? src_of_row[p] / src_div : p) : -1;
+    }
+    __syncthreads();
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += MG_BK) {
+        const int k = k0 + lk;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = lr + 16 * i;
+            const int s = src_s[r], n = n0 + r;
+            As[lk][r] = (s >= 0 && k < K) ? to_f32(A[(size_t)s * lda + k]) : 0.f;
+            Ws[lk][r] = (n < N && k < K) ? to_f32(We[(size_t)n * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MG_BK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty + 16 * i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx + 16 * j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty + 16 * i;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx + 16 * j;
+            float v = acc[i][j];
+            if (gated) {
+                // columns come as 8 gates, then their 8 ups: the up of this thread's gate is 8 lanes on
+                const float up = __shfl_xor_sync(0xffffffffu, v, 8);
+                if (tx < 8 && r < rows && n < N)
+                    C[(size_t)(row0 + r) * ldc + (n >> 4) * 8 + tx] = from_f32<TC>(activation(v, act) * up);
+            } else if (r < rows && n < N) {
+                C[(size_t)(row0 + r) * ldc + n] = from_f32<TC>(v);
+            }
+        }
+    }
+}
+
+// ---- grouped product on the tensor cores (bfloat16 operands, float32 accumulators) ----
+// A block of 4 warps owns a tile of 64 rows x 64 columns; warp w takes rows 32 * (w & 1) and
+// columns 32 * (w >> 1).  k runs in steps of 32 through two shared-memory stages filled by
+// 16-byte asynchronous copies (rows that do not exist are zero).  K a multiple of 8.
+#define MT_BM 64
+#define MT_BN 64
+#define MT_BK 32
+#define MT_LD (MT_BK + 8)   // (a row of 80 bytes: the 8 rows of a matrix load miss each other's banks)
+
+template <typename TC>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ src_of_row, int src_div,
+                    const bf16* __restrict__ W, const int* __restrict__ tiles, const int* __restrict__ n_tiles,
+                    TC* __restrict__ C, int ldc, int N, int K, int gated, int act) {
+    __shared__ __align__(16) bf16 As[2][MT_BM][MT_LD];
+    __shared__ __align__(16) bf16 Ws[2][MT_BN][MT_LD];
+    __shared__ int src_s[MT_BM];
+    pdl_wait();
+    pdl_trigger();
+    if ((int)blockIdx.y >= n_tiles[0]) return;
+    const int e = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    const bf16* We = W + (size_t)e * N * K;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * MT_BN;
+    if (tid < MT_BM) {
+        const int p = row0 + tid;
+        src_s[tid] = tid < rows ? (src_of_row ? src_of_row[p] / src_div : p) : -1;
+    }
+    __syncthreads();
+    const int wm = (warp & 1) * 32, wn = (warp >> 1) * 32;
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+
+    auto load_stage = [&](int stage, int k0) {
+        // 64 rows x 4 chunks of 8 elements per operand; 128 threads take 2 chunks of each
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int idx = tid + it * 128;
+            const int r = idx >> 2, ck = (idx & 3) * 8;
+            const int k = k0 + ck;
+            bf16* da = &As[stage][r][ck];
+            const int s = src_s[r];
+            if (s >= 0 && k < K) cp_async16(da, A + (size_t)s * lda + k);
+            else *reinterpret_cast<uint4*>(da) = make_uint4(0, 0, 0, 0);
+            bf16* dw = &Ws[stage][r][ck];
+            const int n = n0 + r;
+            if (n < N && k < K) cp_async16(dw, We + (size_t)n * K + k);
+            else *reinterpret_cast<uint4*>(dw) = make_uint4(0, 0, 0, 0);
+        }
+        cp_async_commit();
+    };
+
+    const int nk = (K + MT_BK - 1) / MT_BK;
+    load_stage(0, 0);
+    for (int kb = 0; kb < nk; ++kb) {
+        const int cur = kb & 1;
+        if (kb + 1 < nk) { load_stage(cur ^ 1, (kb + 1) * MT_BK); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < MT_BK; ks += 16) {
+            unsigned a[2][4], b[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix_x4(a[i][0], a[i][1], a[i][2], a[i][3], &As[cur][wm + 16 * i + (lane & 15)][ks + (lane >> 4) * 8]);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                // two n-tiles of 8 columns at once: matrices (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+                unsigned r0, r1, r2, r3;
+                ldmatrix_x4(r0, r1, r2, r3, &Ws[cur][wn + 16 * j + (lane & 7) + ((lane >> 4) << 3)][ks + ((lane >> 3) & 1) * 8]);
+                b[2 * j][0] = r0; b[2 * j][1] = r1; b[2 * j + 1][0] = r2; b[2 * j + 1][1] = r3;
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], a[i], b[j][0], b[j][1]);
+        }
+        __syncthreads();
+    }
+    // accumulator layout of m16n8: c0,c1 at (row lane/4, cols 2*(lane%4), +1); c2,c3 eight rows further down
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm + 16 * i + (lane >> 2) + 8 * half;
+            if (r >= rows) continue;
+            TC* crow = C + (size_t)(row0 + r) * ldc;
+            if (gated) {
+#pragma unroll
+                for (int j = 0; j < 4; j += 2) {   // n-tile j: 8 gates, n-tile j + 1: their ups
+                    const int n = n0 + wn + 8 * j + 2 * (lane & 3);
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+                        if (n + c < N)
+                            crow[((n + c) >> 4) * 8 + ((n + c) & 7)] =
+                                from_f32<TC>(activation(acc[i][j][2 * half + c], act) * acc[i][j + 1][2 * half + c]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int n = n0 + wn + 8 * j + 2 * (lane & 3);
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+                        if (n + c < N) crow[n + c] = from_f32<TC>(acc[i][j][2 * half + c]);
+                }
+            }
+        }
+    }
+}
+
+// in_dtype: A and W; out_dtype: C.  `tensor_cores`: the bfloat16 kernel (K a multiple of 8,
+// 16-byte aligned rows); else the multiply-add kernel.  max_tiles bounds the tiles of any step.
+extern "C" int vx_moe_gemm(const void* A, int lda, const int* src_of_row, int src_div, const void* W, const int* tiles,
+                           const int* n_tiles, int max_tiles, void* C, int ldc, int N, int K, int gated, int act,
+                           int in_dtype, int out_dtype, int tensor_cores, cudaStream_t stream) {
+    if (max_tiles <= 0 || N <= 0) return VX_OK;
+    if (K <= 0 || lda < K || src_div <= 0 || (gated && N % 16)) return VX_ERR_SHAPE;
+    if (max_tiles > 65535) return VX_ERR_LIMIT;
+    dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
+    if (tensor_cores) {
+        if (in_dtype != VX_BF16) return VX_ERR_DTYPE;
+        if (K % 8 || lda % 8 || (((uintptr_t)A) | ((uintptr_t)W)) & 15) return VX_ERR_ALIGN;
+        if (out_dtype == VX_BF16)
+            VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_mma_kernel<bf16>), grid, 128, 0, stream, (const bf16*)A, lda, src_of_row, src_div,
+                        (const bf16*)W, tiles, n_tiles, (bf16*)C, ldc, N, K, gated, act);
+        else if (out_dtype == VX_F32)
+            VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_mma_kernel<float>), grid, 128, 0, stream, (const bf16*)A, lda, src_of_row, src_div,
+                        (const bf16*)W, tiles, n_tiles, (float*)C, ldc, N, K, gated, act);
+        else
+            return VX_ERR_DTYPE;
+    } else if (in_dtype == VX_F32 && out_dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_simt_kernel<float, float>), grid, 256, 0, stream, (const float*)A, lda, src_of_row,
+                    src_div, (const float*)W, tiles, n_tiles, (float*)C, ldc, N, K, gated, act);
+    else if (in_dtype == VX_BF16 && out_dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_simt_kernel<bf16, bf16>), grid, 256, 0, stream, (const bf16*)A, lda, src_of_row,
+                    src_div, (const bf16*)W, tiles, n_tiles, (bf16*)C, ldc, N, K, gated, act);
+    else if (in_dtype == VX_BF16 && out_dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_simt_kernel<bf16, float>), grid, 256, 0, stream, (const bf16*)A, lda, src_of_row,
+                    src_div, (const bf16*)W, tiles, n_tiles, (float*)C, ldc, N, K, gated, act);
+    else
+        return VX_ERR_DTYPE;
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// out[t, :] = sum over k (ascending) of weight[t, k] * y[row_of[t * top + k], :] (+ shared[t, :]).
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of,
+                                   const float* __restrict__ weight, const T* __restrict__ shared_out,
+                                   T* __restrict__ out, int width, int top) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; ++k)
+            s = fmaf(weight[(size_t)t * top + k], y[(size_t)row_of[(size_t)t * top + k] * width + i], s);
+        if (shared_out) s += to_f32(shared_out[(size_t)t * width + i]);
+        out[(size_t)t * width + i] = from_f32<T>(s);
+    }
+}
+
+extern "C" int vx_moe_combine(const float* y, const int* row_of, const float* weight, const void* shared_out, void* out,
+                              int tokens, int width, int top, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VX_OK;
+    if (width <= 0 || top <= 0) return VX_ERR_SHAPE;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<float>), tokens, threads, 0, stream, y, row_of, weight,
+                    (const float*)shared_out, (float*)out, width, top);
+    else if (dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<bf16>), tokens, threads, 0, stream, y, row_of, weight,
+                    (const bf16*)shared_out, (bf16*)out, width, top);
+    else
+        return VX_ERR_DTYPE;
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
 import torch
@@ -70,7 +70,16 @@ def _declare(lib) -> None:
         "vx_gated_act": [P, P, I, I, I, I, I, I, P],
         "vx_add_bias": [P, P, P, I, I, I, P],
         "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
-        "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
+        "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, I, I, F, P],
+        "vx_embedding_pair": [P, P, P, P, P, P, P, P, P, I, I, I, I, c_longlong, c_longlong, I, P],
+        "vx_merge_norm_add_norm": [P, P, P, F, P, P, F, P, F, P, P, I, I, F, I, P],
+        "vx_act": [P, I, P, I, I, I, I, I, P],
+        "vx_gated_rmsnorm": [P, P, I, P, P, I, I, F, I, P],
+        "vx_kv_store": [P, I, I, I, P, P, P, I, I, I, I, I, I, P],
+        "vx_linear_attention_recurrent": [P, I, I, I, I, P, P, P, P, P, I, I, I, I, I, I, P],
+        "vx_moe_route": [P, I, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, P],
+        "vx_moe_gemm": [P, I, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, P],
+        "vx_moe_combine": [P, P, P, P, P, I, I, I, I, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
         "vx_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "vx_gemm_tcgen05_pair": [P, P, P, P, I, I, I, I, I, I, I, I, P, P],
@@ -257,18 +266,221 @@ def attention_head_dim_supported(head_dim: int) -> bool:
 
 def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
                             seq_of_token, positions, scale: float, window: int, num_heads: int,
-                            num_kv_heads: int, head_dim: int, tokens: int) -> torch.Tensor:
+                            num_kv_heads: int, head_dim: int, tokens: int, v_head_dim: int = 0, keep_first: int = 0,
+                            bias_exponent: float = 0.0) -> torch.Tensor:
+    """The general kernel.  `v_head_dim`: size of a value (0: a key's); `keep_first`: with a window, the
+    first positions that stay visible; `bias_exponent` b > 0: head h's scores lose
+    2^(-b (h + 1) / heads) * distance."""
     _dev(q, k_pool, v_pool, block_table, seq_of_token, positions)
+    v_head_dim = int(v_head_dim) or head_dim
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
           "paged_attention: int32 block table [requests, blocks]")
     _need(k_pool.dtype == q.dtype and v_pool.dtype == q.dtype, "paged_attention: pools of the queries' element type")
     _need(attention_head_dim_supported(head_dim),
           "paged_attention: head size %d (the kernels take even sizes up to %d)" % (head_dim, ATTENTION_MAX_HEAD_DIM))
-    out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _need(attention_head_dim_supported(v_head_dim) or v_head_dim == head_dim,
+          "paged_attention: value size %d (the kernels take even sizes up to %d)" % (v_head_dim, ATTENTION_MAX_HEAD_DIM))
+    out = torch.empty((tokens, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
     _check(library().vx_paged_attention_generic(
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
-        _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * head_dim, float(scale), int(window), tokens,
-        num_heads, num_kv_heads, head_dim, k_pool.shape[2], dtype_code(q.dtype), _stream()), "paged_attention_generic")
+        _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * v_head_dim, float(scale), int(window), tokens,
+        num_heads, num_kv_heads, head_dim, k_pool.shape[2], dtype_code(q.dtype), v_head_dim, int(keep_first),
+        float(bias_exponent), _stream()), "paged_attention_generic")
+    return out
+
+
+def embedding_pair(ids, positions, seq_of_token, cu_seqlens, state_slots, last_token: torch.Tensor,
+                   table: torch.Tensor, pair_table: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """float32 rows table[id] + pair_table[(previous id * mul_prev + id * mul_cur) mod buckets] (row `buckets`
+    at position 0).  The id before a step's first is read from `last_token` [slots] (int32), which then
+    takes the request's last id of this step."""
+    _dev(ids, positions, seq_of_token, cu_seqlens, state_slots, last_token, table, pair_table)
+    _need(ids.dtype == torch.int32 and last_token.dtype == torch.int32 and last_token.is_contiguous(),
+          "embedding_pair: int32 ids and last tokens")
+    _need(table.is_contiguous() and pair_table.is_contiguous() and table.dtype == pair_table.dtype
+          and pair_table.shape == (buckets + 1, table.shape[1]), "embedding_pair: tables [V,E] and [buckets+1,E]")
+    t, (v, e) = ids.numel(), table.shape
+    out = torch.empty((t, e), dtype=torch.float32, device=table.device)
+    _check(library().vx_embedding_pair(_ptr(ids), _ptr(positions), _ptr(seq_of_token), _ptr(cu_seqlens), _ptr(state_slots),
+                                       _ptr(last_token), _ptr(table), _ptr(pair_table), _ptr(out), t, e, v, int(buckets),
+                                       int(mul_prev), int(mul_cur), dtype_code(table.dtype), _stream()), "embedding_pair")
+    return out
+
+
+def merge_norm_add_norm(residual: torch.Tensor, y0: torch.Tensor, w_post: torch.Tensor, mult: float, eps: float,
+                        w0=None, c0: float = 1.0, y1=None, w1=None, c1: float = 1.0, w_next=None):
+    """residual (float32, in place) += mult * rmsnorm(u) * w_post, with u = y0, or with two branches
+    u = c0 rmsnorm(y0) w0 + c1 rmsnorm(y1) w1.  Returns rmsnorm(residual) * w_next in y0's element type
+    if `w_next` is given, else None."""
+    _dev(residual, y0, w_post, w0, y1, w1, w_next)
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and y0.is_contiguous()
+          and y0.shape == residual.shape, "merge_norm_add_norm: float32 residual, a branch of its shape")
+    width = residual.shape[-1]
+    for w in (w_post, w0, w1, w_next):
+        if w is not None:
+            _need(w.dtype == torch.float32 and w.numel() == width, "merge_norm_add_norm: float32 weights of the row's width")
+    if y1 is not None:
+        _need(y1.is_contiguous() and y1.shape == y0.shape and y1.dtype == y0.dtype and w0 is not None and w1 is not None,
+              "merge_norm_add_norm: two branches of one shape, each with its weight")
+    out = torch.empty_like(y0) if w_next is not None else None
+    _check(library().vx_merge_norm_add_norm(_ptr(residual), _ptr(y0), _ptr(w0), float(c0), _ptr(y1), _ptr(w1), float(c1),
+                                            _ptr(w_post), float(mult), _ptr(w_next), _ptr(out), residual.shape[0], width,
+                                            float(eps), dtype_code(y0.dtype), _stream()), "merge_norm_add_norm")
+    return out
+
+
+def merge_norms(y0: torch.Tensor, w0: torch.Tensor, c0: float, y1: torch.Tensor, w1: torch.Tensor, c1: float,
+                eps: float) -> torch.Tensor:
+    """c0 rmsnorm(y0) w0 + c1 rmsnorm(y1) w1, in the branches' element type."""
+    _dev(y0, w0, y1, w1)
+    width = y0.shape[-1]
+    _need(y0.is_contiguous() and y1.is_contiguous() and y0.shape == y1.shape and y0.dtype == y1.dtype
+          and w0.dtype == torch.float32 and w1.dtype == torch.float32 and w0.numel() == width and w1.numel() == width,
+          "merge_norms: two branches of one shape, float32 weights of the row's width")
+    out = torch.empty_like(y0)
+    _check(library().vx_merge_norm_add_norm(None, _ptr(y0), _ptr(w0), float(c0), _ptr(y1), _ptr(w1), float(c1), None, 1.0,
+                                            None, _ptr(out), y0.shape[0], width, float(eps), dtype_code(y0.dtype), _stream()),
+           "merge_norms")
+    return out
+
+
+def act(x: torch.Tensor, activation: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """activation(x), element by element; x [rows, width] with contiguous rows."""
+    _dev(x)
+    _need(x.dim() == 2 and x.stride(1) == 1, "act: rows must be contiguous")
+    _need(activation in ACTIVATIONS, "act: activation %r is not one of %s" % (activation, sorted(ACTIVATIONS)))
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    _check(library().vx_act(_ptr(x), x.stride(0), _ptr(out), x.shape[0], x.shape[1], ACTIVATIONS[activation],
+                            dtype_code(x.dtype), dtype_code(out.dtype), _stream()), "act")
+    return out
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """rmsnorm(o) * weight * sigmoid(gate): o float32 [rows, width]; gate [rows, width] with contiguous rows
+    in the element type of the result."""
+    _dev(o, gate, weight)
+    _need(o.dtype == torch.float32 and o.is_contiguous() and gate.stride(1) == 1 and gate.shape == o.shape
+          and weight.dtype == torch.float32 and weight.numel() == o.shape[1], "gated_rmsnorm: shapes and element types")
+    out = torch.empty(o.shape, dtype=gate.dtype, device=o.device)
+    _check(library().vx_gated_rmsnorm(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), o.shape[0], o.shape[1],
+                                      float(eps), dtype_code(gate.dtype), _stream()), "gated_rmsnorm")
+    return out
+
+
+def kv_store(x: torch.Tensor, k_col: int, v_col: int, slot_mapping, k_pool, v_pool) -> None:
+    """Keys [Hk, Dk] at column `k_col` and values [Hk, Dv] at column `v_col` of every row of the packed
+    projection `x` into the pools [pages, Hk, S, Dk] and [pages, Hk, S, Dv]."""
+    _dev(x, slot_mapping, k_pool, v_pool)
+    _need(x.stride(1) == 1 and k_pool.dtype == x.dtype and v_pool.dtype == x.dtype and k_pool.is_contiguous()
+          and v_pool.is_contiguous() and k_pool.shape[:3] == v_pool.shape[:3], "kv_store: pools of the rows' element type")
+    _check(library().vx_kv_store(_ptr(x), x.stride(0), int(k_col), int(v_col), _ptr(slot_mapping), _ptr(k_pool), _ptr(v_pool),
+                                 x.shape[0], k_pool.shape[1], k_pool.shape[3], v_pool.shape[3], k_pool.shape[2],
+                                 dtype_code(x.dtype), _stream()), "kv_store")
+
+
+def linear_attention_recurrent(x: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor,
+                               state: torch.Tensor, cu_seqlens, state_slots, seqs: int, heads: int, dim: int,
+                               vdim: int, silu: bool = True) -> torch.Tensor:
+    """Per head S = decay S + k v^T, o = S^T q over every request's tokens in order; q, k [heads, dim] and
+    v [heads, vdim] at columns of the packed projection `x`; `state` float32 [slots, heads, dim, vdim] is
+    read and written back.  Returns float32 [tokens, heads * vdim]."""
+    _dev(x, decay, state, cu_seqlens, state_slots)
+    _need(x.stride(1) == 1 and decay.dtype == torch.float32 and decay.numel() == heads, "linear_attention: float32 decay per head")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+          "linear_attention: float32 state [slots, heads, dim, vdim]")
+    out = torch.empty((x.shape[0], heads * vdim), dtype=torch.float32, device=x.device)
+    _check(library().vx_linear_attention_recurrent(_ptr(x), x.stride(0), int(q_col), int(k_col), int(v_col), _ptr(decay),
+                                                   _ptr(state), _ptr(cu_seqlens), _ptr(state_slots), _ptr(out), int(seqs),
+                                                   heads, dim, vdim, 1 if silu else 0, dtype_code(x.dtype), _stream()),
+           "linear_attention_recurrent")
+    return out
+
+
+LINEAR_ATTENTION_MAX_DIM = 256
+
+
+def linear_attention(x: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
+                     cu_seqlens, state_slots, seqs: int, max_new: int, heads: int, dim: int, vdim: int,
+                     silu: bool = True) -> torch.Tensor:
+    """Decayed linear attention of a step's tokens against the requests' states (see
+    `linear_attention_recurrent`); `max_new` bounds the tokens of any request."""
+    return linear_attention_recurrent(x, q_col, k_col, v_col, decay, state, cu_seqlens, state_slots, seqs, heads, dim,
+                                      vdim, silu)
+
+
+MOE_TILE_ROWS = 64
+
+
+class MoePlan:
+    """What `moe_route` leaves on the device for the grouped products and the combination."""
+    __slots__ = ("chosen", "weight", "tiles", "n_tiles", "src_of_row", "row_of", "max_tiles", "top", "assignments")
+
+
+_MOE_COUNTS = {}
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias, experts: int, top: int) -> MoePlan:
+    """Router logits in float32, the `top` largest per token, softmax over the chosen; then every
+    assignment's row in expert order and the row tiles of the grouped products."""
+    _dev(h, w_router, bias)
+    _need(h.stride(1) == 1 and w_router.dtype == torch.float32 and w_router.is_contiguous()
+          and tuple(w_router.shape) == (experts, h.shape[1]), "moe_route: float32 router [experts, width]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == experts, "moe_route: float32 bias per expert")
+    t, dev = h.shape[0], h.device
+    a = t * top
+    plan = MoePlan()
+    plan.top, plan.assignments = top, a
+    plan.max_tiles = -(-a // MOE_TILE_ROWS) + experts
+    ints = torch.empty(3 * a + (experts + 1) + 3 * plan.max_tiles + 1 + a, dtype=torch.int32, device=dev)
+    plan.chosen, pos, plan.src_of_row, plan.row_of = ints[:a], ints[a:2 * a], ints[2 * a:3 * a], ints[3 * a:4 * a]
+    rest = ints[4 * a:]
+    offsets, plan.tiles, plan.n_tiles = rest[:experts + 1], rest[experts + 1:experts + 1 + 3 * plan.max_tiles], rest[-1:]
+    plan.weight = torch.empty((t, top), dtype=torch.float32, device=dev)
+    key = (str(dev), experts)
+    counts = _MOE_COUNTS.get(key)
+    if counts is None or torch.cuda.is_current_stream_capturing():
+        counts = torch.zeros(experts, dtype=torch.int32, device=dev)   # (the plan kernel leaves it zero again)
+        if not torch.cuda.is_current_stream_capturing():
+            _MOE_COUNTS[key] = counts
+    _check(library().vx_moe_route(_ptr(h), h.stride(0), _ptr(w_router), _ptr(bias), t, h.shape[1], experts, top,
+                                  MOE_TILE_ROWS, _ptr(plan.chosen), _ptr(plan.weight), _ptr(counts), _ptr(pos), _ptr(offsets),
+                                  _ptr(plan.tiles), _ptr(plan.n_tiles), _ptr(plan.src_of_row), _ptr(plan.row_of),
+                                  dtype_code(h.dtype), _stream()), "moe_route")
+    return plan
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gather: bool, out_dtype: torch.dtype,
+             gated_activation: Optional[str] = None) -> torch.Tensor:
+    """Grouped product in expert order: row p of the result is a[src(p)] times w[expert of p] transposed, with
+    w [experts, N, K]; src(p) is the token of assignment p (`gather`) or p itself.  With `gated_activation`,
+    w's rows come in tiles of 8 gate rows followed by their 8 up rows and the result is act(gate) * up."""
+    _dev(a, w)
+    _need(a.stride(1) == 1 and w.is_contiguous() and w.dim() == 3 and w.shape[2] == a.shape[1] and a.dtype == w.dtype,
+          "moe_gemm: a [rows, K], w [experts, N, K] of one element type")
+    n, k = w.shape[1], w.shape[2]
+    cols = n // 2 if gated_activation else n
+    out = torch.empty((plan.assignments, cols), dtype=out_dtype, device=a.device)
+    tc = (a.dtype == torch.bfloat16 and k % 8 == 0 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+          and w.data_ptr() % 16 == 0)
+    _check(library().vx_moe_gemm(_ptr(a), a.stride(0), _ptr(plan.src_of_row) if gather else None, plan.top if gather else 1,
+                                 _ptr(w), _ptr(plan.tiles), _ptr(plan.n_tiles), plan.max_tiles, _ptr(out), cols, n, k,
+                                 1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0), dtype_code(a.dtype),
+                                 dtype_code(out_dtype), 1 if tc else 0, _stream()), "moe_gemm")
+    return out
+
+
+def moe_combine(y: torch.Tensor, plan: MoePlan, shared_out, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per token the weighted sum of its experts' rows of `y` (float32, expert order), plus `shared_out`."""
+    _dev(y, shared_out)
+    _need(y.dtype == torch.float32 and y.is_contiguous(), "moe_combine: float32 rows")
+    t = plan.assignments // plan.top
+    if shared_out is not None:
+        _need(shared_out.dtype == out_dtype and shared_out.is_contiguous() and tuple(shared_out.shape) == (t, y.shape[1]),
+              "moe_combine: the shared expert's output in the result's shape and element type")
+    out = torch.empty((t, y.shape[1]), dtype=out_dtype, device=y.device)
+    _check(library().vx_moe_combine(_ptr(y), _ptr(plan.row_of), _ptr(plan.weight), _ptr(shared_out), _ptr(out), t, y.shape[1],
+                                    plan.top, dtype_code(out_dtype), _stream()), "moe_combine")
     return out
 
 

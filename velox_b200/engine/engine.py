@@ -23,7 +23,7 @@ from ..config.engine_config import EngineConfig
 from ..config.model_config import ModelConfig
 from ..config.registry import load_config, resolve_architecture
 from ..models.decoder import DecoderModel
-from ..cache.kinds import cache_kind
+from ..cache.kinds import CacheParts, cache_kind
 from ..parts.base import Runtime
 from ..sampling.params import SamplingParams
 from ..sampling.rng import uniform
@@ -112,7 +112,8 @@ class Engine:
         if cfg.max_cache_tokens:
             return -(-int(cfg.max_cache_tokens) // cfg.page_size)
         elt = 2 if self.runtime.dtype == torch.bfloat16 else 4
-        kinds = [(cache_kind(s), s) for s in specs if s is not None]
+        flat = [m for s in specs for m in (s.parts if isinstance(s, CacheParts) else (s,))]
+        kinds = [(cache_kind(s), s) for s in flat if s is not None]
         per_page = sum(k.page_bytes(s, cfg.page_size, elt) for k, s in kinds if k.paged)
         wanted = cfg.max_running_requests * max_blocks
         if per_page == 0:

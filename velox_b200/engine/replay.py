@@ -28,7 +28,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=16)
-    ap.add_argument("--max-requests", type=int, default=8, help="requests that may be live at once")
+    ap.add_argument("--max-requests", type=int, default=4,
+                    help="requests that may be live at once (state slots; they are used again as requests end)")
     ap.add_argument("--poison-cache", action="store_true",
                     help="fill the cache pool with NaN first, so that a read of a stale or foreign slot shows")
     return ap

@@ -1,4 +1,4 @@
-from . import qwen3  # registers the architecture
+from . import dobepel, qwen3  # register the architectures
 from .decoder import DecoderModel
 
-__all__ = ["DecoderModel", "qwen3"]
+__all__ = ["DecoderModel", "dobepel", "qwen3"]

@@ -24,7 +24,7 @@ class DecoderModel:
             self.blocks.append(block_cls(
                 build_part("mixer", spec.mixer) if spec.mixer is not None else None,
                 build_part("feed_forward", spec.feed_forward) if spec.feed_forward is not None else None,
-                {name: build_part("norm", n) for name, n in spec.norms.items()}))
+                {name: build_part("norm", n) for name, n in spec.norms.items()}, **spec.block_params))
         self.final_norm = build_part("norm", plan.final_norm)
         self.head = build_part("head", plan.head)
         self.order = plan.running_order()
@@ -56,11 +56,18 @@ class DecoderModel:
     # that the order names twice shares its weights between the two places, but
     # each place keeps keys, values or state of its own, so that a position's
     # result does not depend on how the tokens were cut into steps.
+    # An embedding that keeps something per request has one more place, after the last
+    # of the running order.
     def cache_specs(self) -> list:
         """Per place of the running order: the mixer's cache need, or None for a
-        place without a cache of its own (none at all, or another's)."""
-        return [None if self.plan.layers[i].cache_of is not None or self.blocks[i].mixer is None
-                else self.blocks[i].mixer.cache_spec() for i in self.order]
+        place without a cache of its own (none at all, or another's); then the
+        embedding's need, if it has one."""
+        specs = [None if self.plan.layers[i].cache_of is not None or self.blocks[i].mixer is None
+                 else self.blocks[i].mixer.cache_spec() for i in self.order]
+        return specs + ([self.embedding.cache_spec()] if self._embedding_keeps_state() else [])
+
+    def _embedding_keeps_state(self) -> bool:
+        return getattr(self.embedding, "cache_spec", None) is not None and self.embedding.cache_spec() is not None
 
     def cache_sources(self) -> list:
         """Per place of the running order: None, or the earlier place whose cache
@@ -75,13 +82,16 @@ class DecoderModel:
             if not earlier:
                 raise ValueError("layer %d reads the cache of layer %d, which has not run before it" % (i, j))
             out.append(earlier[-1])
-        return out
+        return out + ([None] if self._embedding_keeps_state() else [])
 
     # -- step ----------------------------------------------------------------
     def forward_hidden(self, ctx, cache):
         """Runs the step's tokens through every layer; returns (residual, delta),
         whose sum is the last layer's output [tokens, hidden]."""
-        residual = self.embedding.forward(ctx)
+        if self._embedding_keeps_state():
+            residual = self.embedding.forward(ctx, cache.layer(len(self.order)))
+        else:
+            residual = self.embedding.forward(ctx)
         delta = None
         for place, i in enumerate(self.order):
             residual, delta = self.blocks[i].forward(residual, delta, ctx, cache.layer(place))

@@ -70,6 +70,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "vxh_slots_create": (P, [I]), "vxh_slots_destroy": (None, [P]), "vxh_slots_num_slots": (I, [P]),
         "vxh_slots_num_free": (I, [P]), "vxh_slots_alloc": (I, [P]), "vxh_slots_free": (I, [P, I]),
         "vxh_cache_create": (P, [I, PI, I, I, I, I]), "vxh_cache_destroy": (None, [P]),
+        "vxh_cache_set_keep_first": (I, [P, I, I]),
         "vxh_cache_pool": (P, [P, I]), "vxh_cache_slots": (P, [P]), "vxh_cache_add": (I, [P, c_int64]), "vxh_cache_has": (I, [P, c_int64]),
         "vxh_cache_num_requests": (L, [P]), "vxh_cache_request_ids": (L, [P, PI64, L]),
         "vxh_cache_length": (L, [P, c_int64]), "vxh_cache_max_length": (L, [P, I, PI64]), "vxh_cache_slot": (I, [P, c_int64]),

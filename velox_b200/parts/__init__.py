@@ -1,20 +1,30 @@
 from .attention import PagedAttention
-from .base import (Block, Embedding, FeedForward, FixedState, Mixer, Norm, PagedKV, Part, Position, Runtime, TensorSpec)
-from .block import PreNormBlock
-from .embedding import OutputHead, TokenEmbedding
+from .base import (Block, CacheParts, Embedding, FeedForward, FixedState, Mixer, Norm, PagedKV, Part, Position, Runtime,
+                   TensorSpec)
+from .block import PreNormBlock, SandwichNormBlock
+from .embedding import OutputHead, PairHashEmbedding, TokenEmbedding
 from .linear import Linear, matmul
-from .mlp import GatedMLP
+from .linear_attention import DecayedLinearAttention
+from .mlp import DenseMLP, GatedMLP
+from .moe import RoutedExperts
 from .norm import RMSNorm
+from .parallel import ParallelMixer
 from .plan import LayerSpec, ModelPlan, PartSpec
 from .position import NoPosition, RotaryPosition
 from .registry import (build_part, part_class, register_block, register_feed_forward, register_mixer,
                        register_norm, register_part, register_position, unregister_part)
 
 register_part("mixer", "paged_attention", PagedAttention)
+register_part("mixer", "decayed_linear_attention", DecayedLinearAttention)
+register_part("mixer", "parallel", ParallelMixer)
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "dense_mlp", DenseMLP)
+register_part("feed_forward", "routed_experts", RoutedExperts)
 register_part("norm", "rms_norm", RMSNorm)
 register_part("position", "rotary", RotaryPosition)
 register_part("position", "none", NoPosition)
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "pair_hash_embedding", PairHashEmbedding)
 register_part("head", "linear_head", OutputHead)

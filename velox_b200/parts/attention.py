@@ -12,11 +12,21 @@ here ([Wq; Wk; Wv], rows in that order), which the reference keeps apart
 Everything is a parameter: head counts, head size, whether q/k are normed,
 whether projections are biased, the window (0: all keys), the scale, and the
 position encoding (a `PartSpec` of category "position").
+
+Three more, for designs that put positions into the scores instead of rotating:
+`v_head_dim` (values of another size than keys; the output projection then takes
+heads * v_head_dim), `keep_first` (with a window, the first positions stay visible
+to every later query, at their true distances), and `distance_bias_exponent` b > 0
+(head h's scores lose 2^(-b (h+1) / heads) * (query position - key position) before
+the softmax; 0: no bias).  With any of them the step's keys and values are written by
+the plain store kernel and the attention runs in the kernels that know them
+(`csrc/attention_biased.cu` for bfloat16, the general kernel otherwise); the q/k norm
+and the rotation need v_head_dim == head_dim.  `names` renames the four matrices.
 """
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -46,13 +56,25 @@ class PagedAttention(Mixer):
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  bias: bool = False, qk_norm: bool = True, eps: float = 1e-6, window: int = 0,
-                 position: Optional[PartSpec] = None, scale: Optional[float] = None):
+                 position: Optional[PartSpec] = None, scale: Optional[float] = None, v_head_dim: int = 0,
+                 keep_first: int = 0, distance_bias_exponent: float = 0.0,
+                 names: Sequence[str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight")):
         super().__init__(prefix)
+        self.names = dict(zip(("q_proj", "k_proj", "v_proj", "o_proj"), names))
         if num_heads % num_kv_heads:
             raise ValueError("num_heads %d is not a multiple of num_kv_heads %d" % (num_heads, num_kv_heads))
         if not ops.attention_head_dim_supported(int(head_dim)):
             raise ValueError("%shead_dim %d: the attention kernels take even head sizes up to %d"
                              % (prefix, head_dim, ops.ATTENTION_MAX_HEAD_DIM))
+        self.v_head_dim = int(v_head_dim) or int(head_dim)
+        self.keep_first, self.bias_exponent = int(keep_first), float(distance_bias_exponent)
+        if self.keep_first < 0 or self.bias_exponent < 0:
+            raise ValueError("%skeep_first and distance_bias_exponent must not be negative" % prefix)
+        if self.v_head_dim != int(head_dim) and (qk_norm or position is not None or bias):
+            raise ValueError("%svalues of another size than keys go with plain projections (no q/k norm, rotation, bias)" % prefix)
+        if not ops.attention_head_dim_supported(self.v_head_dim):
+            raise ValueError("%sv_head_dim %d: the attention kernels take even sizes up to %d"
+                             % (prefix, self.v_head_dim, ops.ATTENTION_MAX_HEAD_DIM))
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.head_dim, self.bias, self.qk_norm = int(head_dim), bool(bias), bool(qk_norm)
         self.eps, self.window = float(eps), int(window)
@@ -65,15 +87,24 @@ class PagedAttention(Mixer):
     # -- weights -------------------------------------------------------------
     def _proj_rows(self):
         d = self.head_dim
-        return {"q_proj": self.num_heads * d, "k_proj": self.num_kv_heads * d, "v_proj": self.num_kv_heads * d}
+        return {"q_proj": self.num_heads * d, "k_proj": self.num_kv_heads * d, "v_proj": self.num_kv_heads * self.v_head_dim}
+
+    def _w(self, name: str) -> str:
+        return self.prefix + self.names[name]
+
+    @property
+    def extended(self) -> bool:
+        """True if the layer uses what only the kernels for biased, unequal or kept-first attention know."""
+        return self.v_head_dim != self.head_dim or self.keep_first > 0 or self.bias_exponent > 0
+
 
     def tensor_specs(self) -> List[TensorSpec]:
         p, specs = self.prefix, []
         for name, rows in self._proj_rows().items():
-            specs.append(TensorSpec(p + name + ".weight", (rows, self.hidden_size), "matrix"))
+            specs.append(TensorSpec(self._w(name), (rows, self.hidden_size), "matrix"))
             if self.bias:
                 specs.append(TensorSpec(p + name + ".bias", (rows,), "bias"))
-        specs.append(TensorSpec(p + "o_proj.weight", (self.hidden_size, self.num_heads * self.head_dim), "matrix"))
+        specs.append(TensorSpec(self._w("o_proj"), (self.hidden_size, self.num_heads * self.v_head_dim), "matrix"))
         if self.bias:
             specs.append(TensorSpec(p + "o_proj.bias", (self.hidden_size,), "bias"))
         if self.qk_norm:
@@ -89,10 +120,10 @@ class PagedAttention(Mixer):
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(tensors, runtime)
         p = self.prefix
-        w = torch.cat([tensors[p + n + ".weight"] for n in ("q_proj", "k_proj", "v_proj")], dim=0).contiguous()
+        w = torch.cat([tensors[self._w(n)] for n in ("q_proj", "k_proj", "v_proj")], dim=0).contiguous()
         b = torch.cat([tensors[p + n + ".bias"] for n in ("q_proj", "k_proj", "v_proj")]).contiguous() if self.bias else None
         self.qkv = Linear(w, b)
-        self.out = Linear(tensors[p + "o_proj.weight"], tensors[p + "o_proj.bias"] if self.bias else None)
+        self.out = Linear(tensors[self._w("o_proj")], tensors[p + "o_proj.bias"] if self.bias else None)
         if self.qk_norm:
             self.q_norm_weight, self.k_norm_weight = tensors[p + "q_norm.weight"], tensors[p + "k_norm.weight"]
         if self.position is not None:
@@ -100,7 +131,10 @@ class PagedAttention(Mixer):
 
     # -- cache ---------------------------------------------------------------
     def cache_spec(self):
-        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+        if not self.extended:
+            return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window,
+                       self.v_head_dim if self.v_head_dim != self.head_dim else 0, self.keep_first if self.window else 0)
 
     # -- step ----------------------------------------------------------------
     def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
@@ -108,6 +142,10 @@ class PagedAttention(Mixer):
         group = ctx.groups[cache.group]
         qkv = self.qkv(h)
         slots = group.slot_mapping if cache.writes else None
+        if self.v_head_dim != D:
+            if slots is not None:
+                ops.kv_store(qkv, H * D, (H + Hk) * D, slots, cache.k_pool, cache.v_pool)
+            return self.out(self._attend_extended(qkv, ctx, cache, group))
         rotary = self.position.rotary_table(h.device) if self.position is not None else None
         qw, kw = self.q_norm_weight, self.k_norm_weight
         if self.position is None or rotary is not None:
@@ -127,8 +165,15 @@ class PagedAttention(Mixer):
                 k.copy_(k2)
             ops.qk_norm_rope_kv(qkv, None, None, self.eps, None, 0, ctx.positions, slots,
                                 cache.k_pool, cache.v_pool, H, Hk, D)
-        attn = self._attend(qkv, ctx, cache, group)
+        attn = self._attend_extended(qkv, ctx, cache, group) if self.extended else self._attend(qkv, ctx, cache, group)
         return self.out(attn)
+
+    def _attend_extended(self, qkv, ctx, cache, group) -> torch.Tensor:
+        H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
+        return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
+                                           ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
+                                           qkv.shape[0], v_head_dim=self.v_head_dim, keep_first=self.keep_first,
+                                           bias_exponent=self.bias_exponent)
 
     def _attend(self, qkv, ctx, cache, group) -> torch.Tensor:
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim

@@ -8,12 +8,14 @@ part knows which model it is in.
                   bind(tensors, runtime) -> takes them (already on the device)
     Norm          forward(x) ; add_norm(residual, delta) -> normed
     Position      an encoding of positions that a mixer applies to q and k
-    Mixer         cache_spec() -> PagedKV | FixedState | a spec of a registered cache kind | None
+    Mixer         cache_spec() -> PagedKV | FixedState | a spec of a registered cache kind |
+                                  CacheParts of several of these | None
                   forward(h, ctx, cache) -> y          h, y: [tokens, hidden]
     FeedForward   forward(h, ctx) -> y
     Block         forward(residual, delta, ctx, cache) -> (residual, delta)
                   built from a mixer, a feed-forward (or None) and norms by name
     Embedding     forward(ctx) -> float32 residual [tokens, hidden]
+                  (forward(ctx, cache) if its cache_spec() asks for per-request state)
 
 `h` and `y` have the engine's element type; the residual stream is float32.
 `ctx` is the step's `StepContext` (engine/batch.py): positions, which request
@@ -35,6 +37,7 @@ class TensorSpec:
       matrix, table: N(0, 0.02); held in the engine's element type
       norm:          1 + N(0, 0.05); held in float32 (an exact widening)
       bias:          N(0, 0.02); held in float32
+      matrix_f32:    N(0, 0.02); held in float32 whatever the engine's element type (a router)
       int_table:     integers; held as int32"""
     name: str
     shape: Tuple[int, ...]
@@ -50,10 +53,18 @@ class Runtime:
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values of every position in pages; with a window only the last
-    `window` positions are ever read, and older pages are given back."""
+    `window` positions are ever read, and older pages are given back, except those
+    that hold one of the first `keep_first` positions (which every query still
+    reads).  `v_head_dim` is the size of a value where it is not a key's (0: the same)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
+    keep_first: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -62,6 +73,14 @@ class FixedState:
     request; zeroed when the slot is handed out."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
+
+
+@dataclass(frozen=True)
+class CacheParts:
+    """The needs of a mixer that is made of several: one spec (or None) per
+    member, in the members' order.  The mixer is handed a `LayerCache` whose
+    `parts` are the members' caches."""
+    parts: Tuple[object, ...]
 
 
 class Part:
@@ -125,9 +144,14 @@ class FeedForward(Part):
 class Embedding(Part):
     """What opens a step: the float32 residual stream [tokens, hidden] from the
     step's context (its token ids, and whatever else of the step an input
-    encoding needs: positions, the request of each token)."""
+    encoding needs: positions, the request of each token).  An embedding that keeps
+    something per request (the token before a step's first one, say) asks for it
+    with `cache_spec()` like a mixer and is then called as `forward(ctx, cache)`."""
 
-    def forward(self, ctx) -> torch.Tensor:
+    def cache_spec(self):
+        return None
+
+    def forward(self, ctx, cache=None) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -139,8 +163,11 @@ class Block:
     needs_mixer = True
     needs_feed_forward = True
 
-    def __init__(self, mixer: Optional[Mixer], feed_forward: Optional[FeedForward], norms: Dict[str, Norm]):
+    def __init__(self, mixer: Optional[Mixer], feed_forward: Optional[FeedForward], norms: Dict[str, Norm],
+                 **params):
         kind = type(self).__name__
+        if params:
+            raise ValueError("%s takes no parameters; the layer's plan gives %s" % (kind, sorted(params)))
         if sorted(norms) != sorted(self.norm_names):
             raise ValueError("%s takes the norms %s; the layer's plan gives %s"
                              % (kind, sorted(self.norm_names), sorted(norms)))

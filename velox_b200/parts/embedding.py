@@ -13,7 +13,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..csrc import ops
-from .base import Embedding, Part, Runtime, TensorSpec
+from .base import Embedding, FixedState, Part, Runtime, TensorSpec
 from .linear import matmul
 
 
@@ -36,27 +36,63 @@ class TokenEmbedding(Embedding):
         return ops.embedding(ctx.token_ids, self.weight)
 
 
+class PairHashEmbedding(Embedding):
+    """x[t] = table[id[t]] + pair_table[(id[t-1] * mul_prev + id[t] * mul_cur) mod buckets]: the token's row
+    plus a row picked by the pair (previous token, token).  A request's first token has no previous one and
+    takes the pair table's last row (number `buckets`).  The token before a step's first is part of the
+    request's state: one int32 per state slot, read and advanced on the device."""
+    cuda_graph_safe = True
+
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, buckets: int, mul_prev: int, mul_cur: int,
+                 table_name: str = "embed", pair_table_name: str = "bigram"):
+        super().__init__(prefix)
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        if self.buckets <= 0 or self.mul_prev < 0 or self.mul_cur < 0:
+            raise ValueError("pair embedding: buckets must be positive and the multipliers not negative")
+        self.table_name, self.pair_table_name = prefix + table_name, prefix + pair_table_name
+        self.weight: Optional[torch.Tensor] = None
+        self.pair_weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.table_name, (self.vocab_size, self.hidden_size), "table"),
+                TensorSpec(self.pair_table_name, (self.buckets + 1, self.hidden_size), "table")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
+        super().bind(tensors, runtime)
+        self.weight, self.pair_weight = tensors[self.table_name], tensors[self.pair_table_name]
+
+    def cache_spec(self):
+        return FixedState((1,), "int32")
+
+    def forward(self, ctx, cache=None) -> torch.Tensor:
+        return ops.embedding_pair(ctx.token_ids, ctx.positions, ctx.seq_of_token, ctx.cu_seqlens, ctx.state_slots,
+                                  cache.state.view(-1), self.weight, self.pair_weight, self.buckets, self.mul_prev,
+                                  self.mul_cur)
+
+
 class OutputHead(Part):
     cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied: bool = False):
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied: bool = False, weight_name: str = "weight"):
         super().__init__(prefix)
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
+        self.weight_name = prefix + weight_name
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
         if self.tied:
             return []
-        return [TensorSpec(self.prefix + "weight", (self.vocab_size, self.hidden_size), "matrix")]
+        return [TensorSpec(self.weight_name, (self.vocab_size, self.hidden_size), "matrix")]
 
     def ignored_tensors(self) -> List[str]:
         # a tied checkpoint may still carry a copy of the head
-        return [self.prefix + "weight"] if self.tied else []
+        return [self.weight_name] if self.tied else []
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(tensors, runtime)
         if not self.tied:
-            self.weight = tensors[self.prefix + "weight"]
+            self.weight = tensors[self.weight_name]
 
     def tie(self, table: torch.Tensor) -> None:
         self.weight = table

@@ -9,7 +9,7 @@ by a kernel of its own).  Activation and product are formed in float32.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -25,8 +25,10 @@ FUSED_TCGEN05_MIN_ROWS = 128
 class GatedMLP(FeedForward):
     cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
 
-    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names: Sequence[str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
         super().__init__(prefix)
+        self.names = tuple(prefix + n for n in names)   # gate, up, down
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         if activation not in ops.ACTIVATIONS:
             raise ValueError("activation %r is not one of %s" % (activation, sorted(ops.ACTIVATIONS)))
@@ -36,14 +38,13 @@ class GatedMLP(FeedForward):
 
     def tensor_specs(self) -> List[TensorSpec]:
         p, e, i = self.prefix, self.hidden_size, self.intermediate_size
-        return [TensorSpec(p + "gate_proj.weight", (i, e), "matrix"),
-                TensorSpec(p + "up_proj.weight", (i, e), "matrix"),
-                TensorSpec(p + "down_proj.weight", (e, i), "matrix")]
+        return [TensorSpec(self.names[0], (i, e), "matrix"), TensorSpec(self.names[1], (i, e), "matrix"),
+                TensorSpec(self.names[2], (e, i), "matrix")]
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(tensors, runtime)
         p = self.prefix
-        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        gate, up = tensors[self.names[0]], tensors[self.names[1]]
         i, e = self.intermediate_size, self.hidden_size
         if i % GATE_TILE == 0:
             self.tile = GATE_TILE
@@ -52,7 +53,7 @@ class GatedMLP(FeedForward):
         else:
             self.tile = 0
             self.gate_up = Linear(torch.cat([gate, up], 0).contiguous())
-        self.down = Linear(tensors[p + "down_proj.weight"])
+        self.down = Linear(tensors[self.names[2]])
 
     def forward(self, h: torch.Tensor, ctx=None) -> torch.Tensor:
         w = self.gate_up.weight
@@ -72,3 +73,32 @@ class GatedMLP(FeedForward):
         else:
             a = ops.gated_act(self.gate_up(h), self.activation, self.tile)
         return self.down(a)
+
+
+class DenseMLP(FeedForward):
+    """down(act(up(x))): two matrices, no gate, no biases.  The activation is taken on the float32 sums
+    of the first product and rounded once."""
+    cuda_graph_safe = True
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "gelu",
+                 names: Sequence[str] = ("up_proj.weight", "down_proj.weight")):
+        super().__init__(prefix)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError("activation %r is not one of %s" % (activation, sorted(ops.ACTIVATIONS)))
+        self.activation = activation
+        self.names = tuple(prefix + n for n in names)   # up, down
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        e, i = self.hidden_size, self.intermediate_size
+        return [TensorSpec(self.names[0], (i, e), "matrix"), TensorSpec(self.names[1], (e, i), "matrix")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
+        super().bind(tensors, runtime)
+        self.up, self.down = Linear(tensors[self.names[0]]), Linear(tensors[self.names[1]])
+
+    def forward(self, h: torch.Tensor, ctx=None) -> torch.Tensor:
+        u = self.up(h, torch.float32)
+        return self.down(ops.act(u, self.activation, out_dtype=h.dtype))

@@ -1,0 +1,88 @@
+"""A routed feed-forward (mixture of experts): every token is sent to the `top` experts whose router logits
+z = W_r h + b are largest and gets sum_e softmax(z over the chosen)_e * expert_e(h); an optional shared
+feed-forward (any registered kind) runs for every token and is added.  An expert is a gated feed-forward
+down(act(gate(h)) * up(h)) without biases.
+
+Nothing of a step comes back to the host: the router kernel leaves the assignments on the device, a plan
+kernel orders them by expert, and two grouped matrix products (gate and up with the activation on their
+accumulators, then down) walk the row tiles of that order; see `csrc/moe.cu`.  The router's matrix is held and
+applied in float32 whatever the engine's element type.  The experts' matrices are stacked at bind time:
+[experts, 2 * inner, hidden] with gate and up rows in tiles of 8 (as `GatedMLP` does for one matrix), and
+[experts, hidden, inner].
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..csrc import ops
+from .base import FeedForward, Runtime, TensorSpec
+from .mlp import GATE_TILE
+from .plan import PartSpec
+from .registry import build_part
+
+
+class RoutedExperts(FeedForward):
+    @property
+    def cuda_graph_safe(self) -> bool:
+        return self.shared is None or bool(self.shared.cuda_graph_safe)
+
+    def __init__(self, prefix: str, hidden_size: int, experts: int, top: int, intermediate_size: int,
+                 activation: str = "silu", router_bias: bool = True, shared: Optional[PartSpec] = None,
+                 router_names: Sequence[str] = ("router", "router.b"), expert_prefix: str = "e%d.",
+                 names: Sequence[str] = ("gate", "up", "down")):
+        super().__init__(prefix)
+        self.hidden_size, self.experts, self.top = int(hidden_size), int(experts), int(top)
+        self.intermediate_size = int(intermediate_size)
+        if not 0 < self.top <= self.experts:
+            raise ValueError("%stop %d of %d experts" % (prefix, self.top, self.experts))
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError("activation %r is not one of %s" % (activation, sorted(ops.ACTIVATIONS)))
+        self.activation, self.router_bias = activation, bool(router_bias)
+        self.router_name, self.bias_name = prefix + router_names[0], prefix + router_names[1]
+        self.expert_names = [tuple(prefix + expert_prefix % e + n for n in names) for e in range(self.experts)]
+        self.shared = build_part("feed_forward", shared) if shared is not None else None
+        self.router = self.bias = self.gate_up = self.down = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        e, i = self.hidden_size, self.intermediate_size
+        specs = [TensorSpec(self.router_name, (self.experts, e), "matrix_f32")]
+        if self.router_bias:
+            specs.append(TensorSpec(self.bias_name, (self.experts,), "bias"))
+        for gate, up, down in self.expert_names:
+            specs += [TensorSpec(gate, (i, e), "matrix"), TensorSpec(up, (i, e), "matrix"), TensorSpec(down, (e, i), "matrix")]
+        return specs + (self.shared.tensor_specs() if self.shared is not None else [])
+
+    def ignored_tensors(self) -> List[str]:
+        return self.shared.ignored_tensors() if self.shared is not None else []
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
+        super().bind(tensors, runtime)
+        e, i = self.hidden_size, self.intermediate_size
+        self.router = tensors[self.router_name]
+        self.bias = tensors[self.bias_name] if self.router_bias else None
+        self.tile = GATE_TILE if i % GATE_TILE == 0 else 0
+        self.gate_up = torch.empty((self.experts, 2 * i, e), dtype=runtime.dtype, device=runtime.device)
+        self.down = torch.empty((self.experts, e, i), dtype=runtime.dtype, device=runtime.device)
+        for x, (gate, up, down) in enumerate(self.expert_names):
+            g, u = tensors[gate], tensors[up]
+            if self.tile:
+                self.gate_up[x] = torch.stack([g.view(i // GATE_TILE, GATE_TILE, e), u.view(i // GATE_TILE, GATE_TILE, e)],
+                                              1).reshape(2 * i, e)
+            else:
+                self.gate_up[x, :i], self.gate_up[x, i:] = g, u
+            self.down[x] = tensors[down]
+        if self.shared is not None:
+            self.shared.bind(tensors, runtime)
+
+    def forward(self, h: torch.Tensor, ctx=None) -> torch.Tensor:
+        plan = ops.moe_route(h, self.router, self.bias, self.experts, self.top)
+        if self.tile:
+            a = ops.moe_gemm(h, self.gate_up, plan, True, h.dtype, gated_activation=self.activation)
+        else:
+            # an inner size that is no multiple of 8: all gates, then all ups; the activation by a kernel of its own
+            a = ops.gated_act(ops.moe_gemm(h, self.gate_up, plan, True, torch.float32), self.activation, 0, out_dtype=h.dtype)
+        y = ops.moe_gemm(a, self.down, plan, False, torch.float32)
+        shared = self.shared.forward(h, ctx) if self.shared is not None else None
+        return ops.moe_combine(y, plan, shared, h.dtype)

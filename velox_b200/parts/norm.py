@@ -16,17 +16,18 @@ from .base import Norm, Runtime, TensorSpec
 class RMSNorm(Norm):
     cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
 
-    def __init__(self, prefix: str, size: int, eps: float):
+    def __init__(self, prefix: str, size: int, eps: float, weight_name: str = "weight"):
         super().__init__(prefix)
         self.size, self.eps = int(size), float(eps)
+        self.weight_name = prefix + weight_name   # (a checkpoint may name the tensor by the prefix alone: "")
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.prefix + "weight", (self.size,), "norm")]
+        return [TensorSpec(self.weight_name, (self.size,), "norm")]
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(tensors, runtime)
-        self.weight = tensors[self.prefix + "weight"]
+        self.weight = tensors[self.weight_name]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps)

@@ -35,6 +35,8 @@ class LayerSpec:
     norms: Dict[str, PartSpec] = field(default_factory=dict)
     block: str = "pre_norm"
     cache_of: Optional[int] = None
+    # constants of the block arrangement (a multiplier of the residual branches, say)
+    block_params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -80,6 +80,6 @@ def bind_random_weights(model, runtime, seed: int) -> None:
 
     def make(name: str) -> torch.Tensor:
         s = specs[name]
-        t = random_tensor(s, seed, torch.float32 if s.role in ("norm", "bias") else runtime.dtype, runtime.device)
+        t = random_tensor(s, seed, torch.float32 if s.role in ("norm", "bias", "matrix_f32") else runtime.dtype, runtime.device)
         return t.to(held_dtype(s.role, t.dtype, runtime)).contiguous()
     model.bind(OnDemand(make, specs), runtime)   # (made when a part binds them: see `load_weights`)
