@@ -1,0 +1,311 @@
+// Paged causal attention with positions in the SCORES instead of a rotation, bfloat16, on
+// the tensor cores: for prompt portions and for single decoded tokens.
+//
+//   score(i, j) = q_i . k_j * scale - slope_h * (i - j),   slope_h = 2^(-bias_exp * (h + 1) / H)
+//   query i sees key j  iff  j <= i and (window == 0 or i - j < window or j < keep_first)
+//   keys of size DK (64, 128), values of size DV (32, 64, 128), which need not be equal
+//
+// grid (query tile, head, segment); 4 warps.  A segment is a request's portion of this step
+// (rows cu_seqlens[s] .. of positions kv_offsets[s] ..), or, for a step of single tokens, one
+// token row with its own position.  A block takes 64 query rows: 64 / G consecutive tokens
+// times the G query heads of one kv head when G is a power of two up to 16 (they share every
+// key/value tile), else 64 tokens of one head; 16 rows per warp, held in registers as A
+// operands.  It walks the tiles of 64 keys that hold kept first positions before the window,
+// then the window's tiles up to the diagonal; K and V tiles are gathered page by page with
+// cp.async into double-buffered, swizzled shared memory.  S = Q K^T by mma.sync.m16n8k16; scale,
+// bias by distance and mask are applied to the float32 sums; running maximum and sum per row in
+// float32 (online softmax, base 2).  The probabilities stay 32-bit in effect: P is cut into
+// bfloat16 halves P = P_hi + P_lo (16 bits of mantissa together) and O += P_hi V + P_lo V.
+//
+// A key slot that the mask hides is never read from a page that may have been given back: its
+// address is clamped to the nearest visible key.  The order of every sum depends only on the
+// query's own position and the request's keys, so a token's result is the same bits in a prompt's
+// portion, alone, or beside other requests.
+#include "common.cuh"
+#include "mma_helpers.cuh"
+
+#define AB_WARPS 4
+#define AB_BM 64
+#define AB_BN 64
+#define AB_LOG2E 1.4426950408889634f
+
+template <int CH> __device__ __forceinline__ int ab_swz(int r, int cc) {
+    // 16-byte chunk cc of row r; rows of 8 or 16 chunks XOR the row's low bits, rows of 4 chunks
+    // (two rows to a 128-byte line) every second row's
+    return CH >= 8 ? (cc ^ (r & 7)) : (cc ^ ((r >> 1) & 3));
+}
+
+struct AbSegments {
+    const int* cu_seqlens;    // portions: rows of segment s are [cu_seqlens[s], cu_seqlens[s + 1])
+    const int* kv_offsets;    //           at positions kv_offsets[s] ..
+    const int* seq_of_token;  // single tokens: segment s is token row s of request seq_of_token[s]
+    const int* positions;     //           at position positions[s]
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(AB_WARPS * 32)
+biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ k_pool,
+                        const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
+                        AbSegments seg, bf16* __restrict__ out, int out_row_stride, float scale_log2, float bias_exp,
+                        int window, int keep_first, int H, int Hk, int S, int share_log2) {
+    extern __shared__ __align__(128) unsigned char ab_smem[];
+    constexpr int KCH = DK / 8, VCH = DV / 8;
+    constexpr int K_BYTES = AB_BN * DK * 2, V_BYTES = AB_BN * DV * 2;
+    pdl_wait();
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = gridDim.x - 1 - blockIdx.x, s = blockIdx.z;   // (the longest tiles first)
+    const int share = 1 << share_log2;
+    const int toks_per_tile = AB_BM >> share_log2;
+    int row_base, n_new, off, seq;
+    if (seg.cu_seqlens) {
+        row_base = seg.cu_seqlens[s];
+        n_new = seg.cu_seqlens[s + 1] - row_base;
+        off = seg.kv_offsets[s];
+        seq = s;
+    } else {
+        row_base = s;
+        n_new = 1;
+        off = seg.positions[s];
+        seq = seg.seq_of_token[s];
+    }
+    const int t0 = qt * toks_per_tile;
+    if (t0 >= n_new) return;
+    const int hk = share > 1 ? blockIdx.y : blockIdx.y / (H / Hk);
+    const int head0 = share > 1 ? hk * share : blockIdx.y;
+    const int* bt = block_table + (size_t)seq * max_blocks;
+    const int toks_live = min(toks_per_tile, n_new - t0);
+    const int kv_hi = off + t0 + toks_live;                              // one past the tile's last visible key
+    const int kv_lo = window > 0 ? max(0, off + t0 + 1 - window) : 0;    // first key of the first row's window
+    const int tile_lo = kv_lo / AB_BN, tile_hi = (kv_hi + AB_BN - 1) / AB_BN;
+    const int kept = window > 0 ? keep_first : 0;
+    const int n_kept_tiles = min((kept + AB_BN - 1) / AB_BN, tile_lo);   // tiles with kept positions, before the window's
+    const int n_tiles = n_kept_tiles + tile_hi - tile_lo;
+
+    unsigned char* q_s = ab_smem;                    // [64][DK]
+    unsigned char* kv_s = ab_smem + AB_BM * DK * 2;  // 2 stages x (K tile, V tile)
+
+    for (int c = threadIdx.x; c < AB_BM * KCH; c += AB_WARPS * 32) {
+        const int r = c / KCH, cc = c % KCH;
+        const int tr = min(t0 + (r >> share_log2), n_new - 1);   // rows past the end repeat the last token
+        const int hd = head0 + (r & (share - 1));
+        cp_async16(q_s + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4),
+                   q + (size_t)(row_base + tr) * q_row_stride + (size_t)hd * DK + cc * 8);
+    }
+    cp_async_commit();
+
+    auto tile_of = [&](int i) { return i < n_kept_tiles ? i : tile_lo + i - n_kept_tiles; };
+    auto issue = [&](int i, int stage) {
+        const int tile = tile_of(i);
+        unsigned char* ks = kv_s + (size_t)stage * (K_BYTES + V_BYTES);
+        unsigned char* vs = ks + K_BYTES;
+        for (int c = threadIdx.x; c < AB_BN * KCH; c += AB_WARPS * 32) {
+            const int r = c / KCH, cc = c % KCH;
+            int key = tile * AB_BN + r;
+            // a hidden slot repeats the nearest key that is not hidden: the kept ones stay where they are,
+            // the others move into [kv_lo, kv_hi) (in a tile before the window: onto the last kept key)
+            if (key >= kept) key = i < n_kept_tiles ? kept - 1 : max(min(key, kv_hi - 1), kv_lo);
+            key = min(key, kv_hi - 1);
+            const int page = bt[key / S];
+            cp_async16(ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4),
+                       k_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DK + cc * 8);
+        }
+        for (int c = threadIdx.x; c < AB_BN * VCH; c += AB_WARPS * 32) {
+            const int r = c / VCH, cc = c % VCH;
+            int key = tile * AB_BN + r;
+            if (key >= kept) key = i < n_kept_tiles ? kept - 1 : max(min(key, kv_hi - 1), kv_lo);
+            key = min(key, kv_hi - 1);
+            const int page = bt[key / S];
+            cp_async16(vs + r * (DV * 2) + (ab_swz<VCH>(r, cc) << 4),
+                       v_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DV + cc * 8);
+        }
+    };
+    issue(0, 0);
+    cp_async_commit();
+
+    cp_async_wait<1>();   // the queries have landed
+    __syncthreads();
+    unsigned qf[DK / 16][4];
+    {
+        const int mi = lane >> 3;
+        const int r = warp * 16 + ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk) {
+            const int cc = 2 * kk + (mi >> 1);
+            ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], q_s + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4));
+        }
+    }
+
+    float o[DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int r0 = warp * 16 + (lane >> 2);
+    const int pos0 = off + t0 + (r0 >> share_log2), pos1 = off + t0 + ((r0 + 8) >> share_log2);
+    const int lo0 = window > 0 ? pos0 + 1 - window : 0, lo1 = window > 0 ? pos1 + 1 - window : 0;
+    const int hd0 = head0 + (r0 & (share - 1)), hd1 = head0 + ((r0 + 8) & (share - 1));
+    const float sl0 = bias_exp > 0.f ? exp2f(-bias_exp * (float)(hd0 + 1) / (float)H) * AB_LOG2E : 0.f;
+    const float sl1 = bias_exp > 0.f ? exp2f(-bias_exp * (float)(hd1 + 1) / (float)H) * AB_LOG2E : 0.f;
+    const int warp_hi = off + t0 + ((warp * 16 + 15) >> share_log2) + 1;
+    const int warp_lo = window > 0 ? off + t0 + ((warp * 16) >> share_log2) + 1 - window : 0;
+
+    for (int i = 0; i < n_tiles; ++i) {
+        const int stage = i & 1;
+        if (i + 1 < n_tiles) issue(i + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const unsigned char* ks = kv_s + (size_t)stage * (K_BYTES + V_BYTES);
+        const unsigned char* vs = ks + K_BYTES;
+        const int key_base = tile_of(i) * AB_BN;
+        if (key_base < warp_hi && (key_base + AB_BN > warp_lo || key_base < kept)) {   // warp-uniform
+            float sc[AB_BN / 16][2][4];
+            bool vis[AB_BN / 16];
+            const int mi = lane >> 3;
+            const int rr = ((mi >> 1) << 3) + (lane & 7);
+#pragma unroll
+            for (int kg = 0; kg < AB_BN / 16; ++kg) {
+                const int key0 = key_base + kg * 16;
+                vis[kg] = key0 < warp_hi && (key0 + 16 > warp_lo || key0 < kept);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sc[kg][0][c] = sc[kg][1][c] = 0.f;
+                if (!vis[kg]) continue;
+                const int r = kg * 16 + rr;
+#pragma unroll
+                for (int kk = 0; kk < DK / 16; ++kk) {
+                    const int cc = 2 * kk + (mi & 1);
+                    unsigned b00, b01, b10, b11;
+                    ldmatrix_x4(b00, b01, b10, b11, ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4));
+                    mma_bf16(sc[kg][0], qf[kk], b00, b01);
+                    mma_bf16(sc[kg][1], qf[kk], b10, b11);
+                }
+            }
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int pos = hrow ? pos1 : pos0, lo = hrow ? lo1 : lo0;
+                const float sl = hrow ? sl1 : sl0;
+                float mx = -INFINITY;
+#pragma unroll
+                for (int kg = 0; kg < AB_BN / 16; ++kg)
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const int key = key_base + kg * 16 + nt * 8 + ((lane & 3) << 1) + c;
+                            const bool ok = vis[kg] && key <= pos && (key >= lo || key < kept);
+                            float& v = sc[kg][nt][2 * hrow + c];
+                            v = ok ? v * scale_log2 - sl * (float)(pos - key) : -INFINITY;
+                            mx = fmaxf(mx, v);
+                        }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m[hrow], mx);
+                const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m[hrow] - m_new);
+                float ps = 0.f;
+#pragma unroll
+                for (int kg = 0; kg < AB_BN / 16; ++kg)
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            float& v = sc[kg][nt][2 * hrow + c];
+                            v = (m_new == -INFINITY) ? 0.f : exp2f(v - m_new);
+                            ps += v;
+                        }
+                l[hrow] = l[hrow] * alpha + ps;
+                m[hrow] = m_new;
+#pragma unroll
+                for (int i2 = 0; i2 < DV / 8; ++i2) {
+                    o[i2][2 * hrow] *= alpha;
+                    o[i2][2 * hrow + 1] *= alpha;
+                }
+            }
+            // O += P V with P = P_hi + P_lo
+#pragma unroll
+            for (int kg = 0; kg < AB_BN / 16; ++kg) {
+                if (!vis[kg]) continue;
+                unsigned hi[4], lw[4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float a = sc[kg][x >> 1][2 * (x & 1)], b = sc[kg][x >> 1][2 * (x & 1) + 1];
+                    const __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
+                    const float2 back = __bfloat1622float2(h2);
+                    hi[x] = *reinterpret_cast<const unsigned*>(&h2);
+                    lw[x] = pack_bf16(a - back.x, b - back.y);
+                }
+                const int r = kg * 16 + ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+                for (int nt = 0; nt < DV / 8; nt += 2) {
+                    const int cc = nt + (mi >> 1);
+                    unsigned v00, v01, v10, v11;
+                    ldmatrix_x4_trans(v00, v01, v10, v11, vs + r * (DV * 2) + (ab_swz<VCH>(r, cc) << 4));
+                    mma_bf16(o[nt], hi, v00, v01);
+                    mma_bf16(o[nt + 1], hi, v10, v11);
+                    mma_bf16(o[nt], lw, v00, v01);
+                    mma_bf16(o[nt + 1], lw, v10, v11);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+        l[hrow] += __shfl_xor_sync(0xffffffffu, l[hrow], 1);
+        l[hrow] += __shfl_xor_sync(0xffffffffu, l[hrow], 2);
+        const int r = r0 + 8 * hrow;
+        const int tok = r >> share_log2;
+        if (tok >= toks_live) continue;
+        const int hd = head0 + (r & (share - 1));
+        const float inv = 1.f / l[hrow];
+        bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)hd * DV + ((lane & 3) << 1);
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt)
+            *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) =
+                __floats2bfloat162_rn(o[nt][2 * hrow] * inv, o[nt][2 * hrow + 1] * inv);
+    }
+}
+
+template <int DK, int DV>
+static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
+                         int max_blocks, AbSegments seg, bf16* out, int out_row_stride, float scale, float bias_exp,
+                         int window, int keep_first, int segments, int max_new, int H, int Hk, int S, cudaStream_t stream) {
+    const size_t smem = (size_t)AB_BM * DK * 2 + 2 * ((size_t)AB_BN * DK * 2 + (size_t)AB_BN * DV * 2);
+    static bool configured[VX_MAX_DEVICES];
+    if (int rc = vx_configure_smem(biased_attention_kernel<DK, DV>, smem, configured)) return rc;
+    const int G = H / Hk;
+    int share_log2 = 0;
+    if (G > 1 && G <= 16 && (G & (G - 1)) == 0)
+        while ((1 << share_log2) < G) ++share_log2;
+    const int toks_per_tile = AB_BM >> share_log2;
+    dim3 grid((max_new + toks_per_tile - 1) / toks_per_tile, share_log2 ? Hk : H, segments);
+    VX_LAUNCH_K(VX_K_ATTENTION, (biased_attention_kernel<DK, DV>), grid, AB_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
+                v_pool, block_table, max_blocks, seg, out, out_row_stride, scale * AB_LOG2E, bias_exp, window, keep_first, H,
+                Hk, S, share_log2);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// Portions: cu_seqlens and kv_offsets given, `segments` requests of up to `max_new` tokens.  Single tokens:
+// cu_seqlens null, seq_of_token and positions given, `segments` token rows (max_new = 1).
+extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
+                                   const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
+                                   const int* seq_of_token, const int* positions, void* out, int out_row_stride,
+                                   float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
+                                   int H, int Hk, int DK, int DV, int S, cudaStream_t stream) {
+    if (segments <= 0 || max_new <= 0) return VX_OK;
+    if (H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
+    if (cu_seqlens ? !kv_offsets : (!seq_of_token || !positions || max_new != 1)) return VX_ERR_SHAPE;
+    if (H > 65535 || segments > 65535) return VX_ERR_LIMIT;
+    if ((q_row_stride & 7) || (((uintptr_t)q) & 15) || (out_row_stride & 1) || (((uintptr_t)out) & 3)) return VX_ERR_ALIGN;
+    AbSegments seg = {cu_seqlens, kv_offsets, seq_of_token, positions};
+#define AB_GO(K_, V_)                                                                                                     \
+    if (DK == K_ && DV == V_)                                                                                             \
+        return launch_biased<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, \
+                                     max_blocks, seg, (bf16*)out, out_row_stride, scale, bias_exp, window, keep_first,    \
+                                     segments, max_new, H, Hk, S, stream)
+    AB_GO(64, 32); AB_GO(64, 64); AB_GO(64, 128); AB_GO(128, 32); AB_GO(128, 64); AB_GO(128, 128);
+#undef AB_GO
+    return VX_ERR_SHAPE;
+}

@@ -71,6 +71,7 @@ def _declare(lib) -> None:
         "vx_add_bias": [P, P, P, I, I, I, P],
         "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, I, I, F, P],
+        "vx_biased_attention": [P, I, P, P, P, I, P, P, P, P, P, I, F, F, I, I, I, I, I, I, I, I, I, P],
         "vx_embedding_pair": [P, P, P, P, P, P, P, P, P, I, I, I, I, c_longlong, c_longlong, I, P],
         "vx_merge_norm_add_norm": [P, P, P, F, P, P, F, P, F, P, P, I, I, F, I, P],
         "vx_act": [P, I, P, I, I, I, I, I, P],
@@ -287,6 +288,52 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
         num_heads, num_kv_heads, head_dim, k_pool.shape[2], dtype_code(q.dtype), v_head_dim, int(keep_first),
         float(bias_exponent), _stream()), "paged_attention_generic")
     return out
+
+
+def biased_attention_supported(dtype, head_dim: int, v_head_dim: int, page_size: int) -> bool:
+    """What the tensor-core kernel for attention with a bias by distance, a window with kept first positions
+    and values of another size than keys takes."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and v_head_dim in (32, 64, 128) and page_size % 16 == 0
+
+
+def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions,
+                      scale, window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, segments,
+                      max_new, tokens, out):
+    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions, out)
+    _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
+          "biased_attention: bfloat16 only")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
+          "biased_attention: int32 block table [requests, blocks]")
+    _need(k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.shape[3] == head_dim and v_pool.shape[3] == v_head_dim,
+          "biased_attention: pools [pages, kv heads, page size, head size]")
+    if out is None:
+        out = torch.empty((tokens, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
+    _check(library().vx_biased_attention(
+        _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(cu_seqlens),
+        _ptr(kv_offsets), _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * v_head_dim, float(scale),
+        float(bias_exponent), int(window), int(keep_first), int(segments), int(max_new), num_heads, num_kv_heads, head_dim,
+        v_head_dim, k_pool.shape[2], _stream()), "biased_attention")
+    return out
+
+
+def biased_prefill_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, scale: float,
+                             window: int, keep_first: int, bias_exponent: float, num_heads: int, num_kv_heads: int,
+                             head_dim: int, v_head_dim: int, requests: int, max_new: int, tokens: int, out=None):
+    """Attention of prompt portions (request i: rows cu_seqlens[i] .. at positions kv_offsets[i] ..) with
+    score = q.k * scale - 2^(-bias_exponent (h+1) / heads) * distance under a window that keeps the first
+    `keep_first` positions; bfloat16, tensor cores, probabilities in two bfloat16 halves."""
+    return _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, None, None, scale,
+                             window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, requests,
+                             max_new, tokens, out)
+
+
+def biased_decode_attention(q, q_row_stride, k_pool, v_pool, block_table, seq_of_token, positions, scale: float,
+                            window: int, keep_first: int, bias_exponent: float, num_heads: int, num_kv_heads: int,
+                            head_dim: int, v_head_dim: int, tokens: int, out=None):
+    """The same for token rows that each stand alone: row t is request seq_of_token[t] at position positions[t]."""
+    return _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, None, None, seq_of_token, positions, scale,
+                             window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, tokens, 1,
+                             tokens, out)
 
 
 def embedding_pair(ids, positions, seq_of_token, cu_seqlens, state_slots, last_token: torch.Tensor,
