@@ -152,8 +152,16 @@ def route(h, w_router, bias, top):
     return chosen, e / e.sum(axis=1, keepdims=True)
 
 
-def routed_ff(h, w, p, c, store=keep):
+def route_margin(h, w_router, bias, top):
+    """Per token the gap between the last chosen logit and the first one left out (inf if none is left out)."""
+    z = -np.sort(-(h @ w_router.T + bias), axis=1)
+    return z[:, top - 1] - z[:, top] if top < z.shape[1] else np.full(h.shape[0], np.inf)
+
+
+def routed_ff(h, w, p, c, store=keep, margins_out=None):
     chosen, weight = route(h, w[p + "router"], w[p + "router.b"], c["router"]["top"])
+    if margins_out is not None:
+        margins_out.append(route_margin(h, w[p + "router"], w[p + "router.b"], c["router"]["top"]))
     out = np.zeros((h.shape[0], w[p + "e0.down"].shape[0]))
     for e in range(c["router"]["experts"]):
         rows, col = np.nonzero(chosen == e)
@@ -164,8 +172,9 @@ def routed_ff(h, w, p, c, store=keep):
     return store(out)
 
 
-def forward(cfg, w, ids, store=keep, layers_out=None):
-    """Logits [T, vocab] of a whole sequence; `layers_out` (a list) gets the residual after every layer."""
+def forward(cfg, w, ids, store=keep, layers_out=None, margins_out=None):
+    """Logits [T, vocab] of a whole sequence; `layers_out` (a list) gets the residual after every layer,
+    `margins_out` (a list) every routed layer's `route_margin`."""
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
     b = cfg["embedding"]["bigram"]
     x = embed(ids, w["embed"], w["bigram"], b["buckets"], b["mul_prev"], b["mul_cur"])
@@ -177,7 +186,7 @@ def forward(cfg, w, ids, store=keep, layers_out=None):
         if layer.get("mlp"):
             h = store(rms_norm(x, w[p + "norm2"], eps))
             f = dense_ff(h, w, p + "mlp.", store) if layer["mlp"]["kind"] == "dense" else \
-                routed_ff(h, w, p + "mlp.", layer["mlp"], store)
+                routed_ff(h, w, p + "mlp.", layer["mlp"], store, margins_out)
             x = x + m * rms_norm(f, w[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.copy())

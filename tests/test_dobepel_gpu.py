@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 import plain_dobepel as D
-from dobepel_helpers import CONFIGS, Oracle, lively_weights, write_model
+from dobepel_helpers import CONFIGS, Oracle, compare, decided_tokens, lively_weights, write_model
 from helpers import RoundingJudge, assert_close
 
 pytestmark = pytest.mark.gpu
@@ -67,17 +67,21 @@ def portions(tokens, sizes, name):
     return steps
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["odd", "even"])
-def test_whole_prompts_portions_and_decoding_agree_with_the_plain_implementation(models, name, dtype):
+# In bfloat16 a router's close call may go the other way, and the other expert's output then reaches every later
+# position; so long bfloat16 runs use the configuration without routers (and the odd one, whose routers have
+# one or all experts to choose), and the routed one runs on a sequence that has no close call.
+@pytest.mark.parametrize("name,dtype,length", [("odd", "float32", 150), ("even", "float32", 150), ("dense", "float32", 150),
+                                               ("odd", "bfloat16", 150), ("dense", "bfloat16", 150), ("even", "bfloat16", 44)])
+def test_whole_prompts_portions_and_decoding_agree_with_the_plain_implementation(models, name, dtype, length):
     cfg, w, folder = models[name]
-    toks = tokens_of(cfg, 150, 1)
-    oracle = Oracle(cfg, w, toks)
+    toks, oracle = decided_tokens(cfg, w, length, 1) if (name, dtype) == ("even", "bfloat16") else (tokens_of(cfg, length, 1), None)
+    oracle = oracle or Oracle(cfg, w, toks)
     judge = RoundingJudge.of([oracle], "dobepel %s %s" % (name, dtype))
     engine = engine_for(folder, dtype, 160 + 64)
     ways = {
         "whole": [[("a", toks, list(range(len(toks))))]],
-        "prompt then one by one": [[("a", toks[:90], list(range(90)))]] + [[("a", [t], [0])] for t in toks[90:]],
+        "prompt then one by one": [[("a", toks[:length * 3 // 5], list(range(length * 3 // 5)))]]
+                                  + [[("a", [t], [0])] for t in toks[length * 3 // 5:]],
         "token by token from the start": [[("a", [t], [0])] for t in toks[:40]],
         "portions 2 3 64 5 1 16 2": portions(toks, [2, 3, 64, 5, 1, 16, 2], "a"),
         "portions 17 31": portions(toks, [17, 31], "a"),
@@ -85,7 +89,7 @@ def test_whole_prompts_portions_and_decoding_agree_with_the_plain_implementation
     }
     for what, steps in ways.items():
         got = np.concatenate([g for g in run(engine, steps + [[("end", "a")]]) if g is not None])
-        assert_close(got, oracle.exact[:len(got)], dtype, "%s, %s" % (name, what), cost=oracle.cost[:len(got)], judge=judge)
+        compare(got, [(oracle, 0, len(got))], dtype, "%s, %s" % (name, what), judge)
     if dtype != "float32":
         judge.finish()
 
@@ -94,7 +98,7 @@ def test_whole_prompts_portions_and_decoding_agree_with_the_plain_implementation
 def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(models, dtype):
     """Four live requests at most in a pool of 20 pages and 3 slots: requests of 1 to 130 tokens come, go on beside
     one another in portions and single tokens, are left out of steps, end, and their pages and slots go to the next."""
-    cfg, w, folder = models["even"]
+    cfg, w, folder = models["even" if dtype == "float32" else "dense"]
     lens = {"a": 130, "b": 37, "c": 1, "d": 64, "e": 90, "f": 2, "g": 70}
     toks = {k: tokens_of(cfg, n, 100 + i) for i, (k, n) in enumerate(lens.items())}
     oracle = {k: Oracle(cfg, w, t) for k, t in toks.items()}
@@ -124,9 +128,7 @@ def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(models, dtype)
             continue
         entries = [take(k, n) for k, n in step]
         got = run(engine, [[(k, t, want) for k, t, want, _ in entries]])[0]
-        want = np.concatenate([oracle[k].exact[lo:lo + len(t)] for k, t, _, lo in entries])
-        cost = np.concatenate([oracle[k].cost[lo:lo + len(t)] for k, t, _, lo in entries])
-        assert_close(got, want, dtype, "step %s" % (step,), cost=cost, judge=judge)
+        compare(got, [(oracle[k], lo, lo + len(t)) for k, t, _, lo in entries], dtype, "step %s" % (step,), judge)
     assert all(at[k] == len(toks[k]) for k in toks)
     assert engine.cache.slots.num_free == 3 and all(g.allocator.num_free == g.allocator.num_pages for g in engine.cache.groups)
     if dtype != "float32":
@@ -151,14 +153,14 @@ def test_the_window_gives_pages_back_but_keeps_those_of_the_first_tokens(models)
 def test_long_decoding(models, dtype):
     """360 tokens one by one after a short prompt: the windows pass over decoded tokens only, the states carry
     hundreds of steps, the captured step is replayed."""
-    cfg, w, folder = models["even"]
+    cfg, w, folder = models["even" if dtype == "float32" else "dense"]
     toks = tokens_of(cfg, 380, 9)
     oracle = Oracle(cfg, w, toks)
     judge = RoundingJudge.of([oracle], "dobepel long decoding %s" % dtype)
     engine = engine_for(folder, dtype, 384)
     steps = [[("a", toks[:20], list(range(20)))]] + [[("a", [t], [0])] for t in toks[20:]]
     got = np.concatenate(run(engine, steps))
-    assert_close(got, oracle.exact, dtype, "long decoding", cost=oracle.cost, judge=judge)
+    compare(got, [(oracle, 0, len(toks))], dtype, "long decoding", judge)
     if dtype != "float32":
         judge.finish()
 

@@ -33,7 +33,7 @@ def close(got, want, tol):
     assert np.abs(got - want).max() <= tol * scale, "largest error %g of scale %g" % (np.abs(got - want).max(), scale)
 
 
-TOL = {torch.float32: 2e-5, torch.bfloat16: 1.5e-2}
+TOL = {torch.float32: 2e-5, torch.bfloat16: 8e-3}   # (a bfloat16 result is rounded once: 2^-8 of its size)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -92,27 +92,30 @@ def test_gated_norm_and_activation(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,Dk,Dv", [(3, 10, 40), (2, 64, 32), (1, 128, 128), (2, 7, 5)])
+@pytest.mark.parametrize("H,Dk,Dv", [(3, 10, 40), (2, 64, 32), (1, 128, 128), (2, 7, 5), (3, 32, 96), (2, 32, 64), (2, 64, 192)])
 def test_decayed_linear_attention_carries_its_state(dtype, H, Dk, Dv):
-    """Three requests of 37, 1 and 70 tokens in portions (one of them token by token) against the whole sequences;
-    a far token's contribution survives hundreds of steps under a decay of 1 and dies under a small one."""
+    """Three requests of 237, 1 and 270 tokens in portions (some of them single tokens) against the whole sequences;
+    a far token's contribution survives hundreds of steps under a decay of 1 and dies under a small one.  In bfloat16
+    the steps with a portion of 32 tokens or more run in the chunked kernel (sizes it takes), the others in the
+    recurrent one: both must carry the same state."""
     from velox_b200.csrc import ops
     rng = np.random.default_rng(Dk)
-    lens = [37, 1, 70]
+    lens = [237, 1, 270]
     decay = np.asarray(([1.0, 0.9, 0.3] * H)[:H])
     W = 2 * H * Dk + H * Dv + 3   # (three columns of something else at the end of the packed rows)
     xs = [bf(rng.normal(size=(n, W))) for n in lens]
     want = []
     for x in xs:
         n = x.shape[0]
-        q, k = D.silu(x[:, :H * Dk]).reshape(n, H, Dk), D.silu(x[:, H * Dk:2 * H * Dk]).reshape(n, H, Dk)
-        v = D.silu(x[:, 2 * H * Dk:2 * H * Dk + H * Dv]).reshape(n, H, Dv)
+        store = bf if dtype == torch.bfloat16 else D.keep   # (a bfloat16 engine stores the activated projections rounded)
+        q, k = store(D.silu(x[:, :H * Dk])).reshape(n, H, Dk), store(D.silu(x[:, H * Dk:2 * H * Dk])).reshape(n, H, Dk)
+        v = store(D.silu(x[:, 2 * H * Dk:2 * H * Dk + H * Dv])).reshape(n, H, Dv)
         want.append(D.decayed_linear_attention(q, k, v, decay)[0].reshape(n, H * Dv))
     state = torch.full((5, H, Dk, Dv), float("nan"), device=DEV)
     slots = [4, 1, 2]
     for s in slots:
         state[s].zero_()
-    cuts = [[20, 1, 1, 15], [1], [2, 33, 1, 34]]
+    cuts = [[20, 1, 1, 215], [1], [2, 133, 1, 134]]
     at, got = [0, 0, 0], [[], [], []]
     for step in range(4):
         rows, cu, sl, who = [], [0], [], []
@@ -131,7 +134,9 @@ def test_decayed_linear_attention_carries_its_state(dtype, H, Dk, Dv):
     for r in range(3):
         g = np.concatenate(got[r])
         scale = np.abs(want[r]).max()
-        assert np.abs(g - want[r]).max() <= 1e-4 * scale, (r, np.abs(g - want[r]).max(), scale)
+        # (bfloat16: the device's silu differs from the host's by an ulp now and then, and rounding then goes the other way)
+        tol = 1e-4 if dtype == torch.float32 else 2e-3
+        assert np.abs(g - want[r]).max() <= tol * scale, (r, np.abs(g - want[r]).max(), scale)
 
 
 def paged(k, v, page_size, n_pages, seed):

@@ -78,6 +78,7 @@ def _declare(lib) -> None:
         "vx_gated_rmsnorm": [P, P, I, P, P, I, I, F, I, P],
         "vx_kv_store": [P, I, I, I, P, P, P, I, I, I, I, I, I, P],
         "vx_linear_attention_recurrent": [P, I, I, I, I, P, P, P, P, P, I, I, I, I, I, I, P],
+        "vx_linear_attention_chunked": [P, I, I, I, I, P, P, P, P, P, I, I, I, I, P],
         "vx_moe_route": [P, I, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, P],
         "vx_moe_gemm": [P, I, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, P],
         "vx_moe_combine": [P, P, P, P, P, I, I, I, I, P],
@@ -446,11 +447,34 @@ def linear_attention_recurrent(x: torch.Tensor, q_col: int, k_col: int, v_col: i
 LINEAR_ATTENTION_MAX_DIM = 256
 
 
+LINEAR_ATTENTION_CHUNKED_MIN_TOKENS = 32   # longest portion of a step from which the chunked kernel is used
+
+
+def linear_attention_chunked_supported(dtype, dim: int, vdim: int) -> bool:
+    return dtype == torch.bfloat16 and dim in (32, 64, 128) and vdim % 32 == 0
+
+
 def linear_attention(x: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
                      cu_seqlens, state_slots, seqs: int, max_new: int, heads: int, dim: int, vdim: int,
                      silu: bool = True) -> torch.Tensor:
     """Decayed linear attention of a step's tokens against the requests' states (see
-    `linear_attention_recurrent`); `max_new` bounds the tokens of any request."""
+    `linear_attention_recurrent`); `max_new` bounds the tokens of any request.  A bfloat16 step with a portion of
+    `LINEAR_ATTENTION_CHUNKED_MIN_TOKENS` tokens or more runs in chunks of 64 tokens on the tensor cores (the
+    activation first, by a kernel of its own, rounded to bfloat16 as the recurrent kernel rounds it)."""
+    width = 2 * heads * dim + heads * vdim
+    if (max_new >= LINEAR_ATTENTION_CHUNKED_MIN_TOKENS and linear_attention_chunked_supported(x.dtype, dim, vdim)
+            and k_col == q_col + heads * dim and v_col == k_col + heads * dim and q_col + width <= x.shape[1]):
+        _dev(x, decay, state, cu_seqlens, state_slots)
+        _need(decay.dtype == torch.float32 and decay.numel() == heads, "linear_attention: float32 decay per head")
+        _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+              "linear_attention: float32 state [slots, heads, dim, vdim]")
+        qkv = act(x[:, q_col:q_col + width], "silu") if silu else x[:, q_col:q_col + width]
+        if qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
+            out = torch.empty((x.shape[0], heads * vdim), dtype=torch.float32, device=x.device)
+            _check(library().vx_linear_attention_chunked(_ptr(qkv), qkv.stride(0), 0, heads * dim, 2 * heads * dim, _ptr(decay),
+                                                         _ptr(state), _ptr(cu_seqlens), _ptr(state_slots), _ptr(out),
+                                                         int(seqs), heads, dim, vdim, _stream()), "linear_attention_chunked")
+            return out
     return linear_attention_recurrent(x, q_col, k_col, v_col, decay, state, cu_seqlens, state_slots, seqs, heads, dim,
                                       vdim, silu)
 
