@@ -68,13 +68,13 @@ def portions(tokens, sizes, name):
 
 
 # In bfloat16 a router's close call may go the other way, and the other expert's output then reaches every later
-# position; so long bfloat16 runs use the configuration without routers (and the odd one, whose routers have
-# one or all experts to choose), and the routed one runs on a sequence that has no close call.
+# position; so long bfloat16 runs use the configuration without routers, and the routed ones run on sequences
+# that have no close call.
 @pytest.mark.parametrize("name,dtype,length", [("odd", "float32", 150), ("even", "float32", 150), ("dense", "float32", 150),
-                                               ("odd", "bfloat16", 150), ("dense", "bfloat16", 150), ("even", "bfloat16", 44)])
+                                               ("odd", "bfloat16", 60), ("dense", "bfloat16", 150), ("even", "bfloat16", 24)])
 def test_whole_prompts_portions_and_decoding_agree_with_the_plain_implementation(models, name, dtype, length):
     cfg, w, folder = models[name]
-    toks, oracle = decided_tokens(cfg, w, length, 1) if (name, dtype) == ("even", "bfloat16") else (tokens_of(cfg, length, 1), None)
+    toks, oracle = decided_tokens(cfg, w, length, 1) if (name, dtype) in (("even", "bfloat16"), ("odd", "bfloat16")) else (tokens_of(cfg, length, 1), None)
     oracle = oracle or Oracle(cfg, w, toks)
     judge = RoundingJudge.of([oracle], "dobepel %s %s" % (name, dtype))
     engine = engine_for(folder, dtype, 160 + 64)

@@ -42,7 +42,7 @@ class DecoderModel:
         return [s for p in self.parts() for s in p.tensor_specs()]
 
     def ignored_tensors(self) -> List[str]:
-        return [n for p in self.parts() for n in p.ignored_tensors()]
+        return [n for p in self.parts() for n in p.ignored_tensors()] + list(self.plan.ignored_tensors)
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         self.runtime = runtime

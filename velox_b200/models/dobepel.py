@@ -55,13 +55,15 @@ def _feed_forward(cfg: DobepelConfig, mlp, p: str):
 
 def dobepel_plan(cfg: DobepelConfig) -> ModelPlan:
     norm = lambda name: PartSpec("rms_norm", name, dict(size=cfg.width, eps=cfg.norm_eps, weight_name=""))
-    layers = []
+    layers, unused = [], []
     for i, layer in enumerate(cfg.layers):
         p = "l%d." % i
         ff = _feed_forward(cfg, layer.get("mlp"), p + "mlp.")
         norms = {"mixer": norm(p + "norm1"), "mixer_out": norm(p + "norm1b")}
         if ff is not None:
             norms.update({"feed_forward": norm(p + "norm2"), "feed_forward_out": norm(p + "norm2b")})
+        else:   # (a layer without a feed-forward has no use for its norms, should a checkpoint carry them)
+            unused += [p + "norm2", p + "norm2b"]
         layers.append(LayerSpec(mixer=_mixer(cfg, layer, p + "mix."), feed_forward=ff, norms=norms, block="sandwich_norm",
                                 block_params=dict(residual_mult=cfg.residual_mult)))
     return ModelPlan(
@@ -71,7 +73,7 @@ def dobepel_plan(cfg: DobepelConfig) -> ModelPlan:
             mul_cur=cfg.bigram_mul_cur, table_name="embed", pair_table_name="bigram")),
         layers=layers, final_norm=norm("final.norm"),
         head=PartSpec("linear_head", "head", dict(vocab_size=cfg.vocab, hidden_size=cfg.width, weight_name="")),
-        order=list(range(len(layers))))
+        order=list(range(len(layers))), ignored_tensors=unused)
 
 
 register_architecture(DobepelConfig.architecture, DobepelConfig.model_type, DobepelConfig, dobepel_plan)

@@ -49,6 +49,8 @@ class ModelPlan:
     head: PartSpec
     order: List[int] = field(default_factory=list)
     max_positions: int = 0
+    # names that a checkpoint may hold and the model does not use (no error to find them)
+    ignored_tensors: List[str] = field(default_factory=list)
 
     def running_order(self) -> List[int]:
         return list(self.order) if self.order else list(range(len(self.layers)))
