@@ -193,6 +193,215 @@ def stream_workload(args, cfg, layers):
             "data": "synthetic: random weights, uniform random token ids, seeded arrivals"}
 
 
+# ---- Dobepel beside Qwen3 at equal size (`--workload dobepel`) ---------------------------------------
+# Layer sizes that resemble a real model's (random weights): width, layers, query / kv heads of the softmax
+# attention (heads of 128, values of 128, window 1,024, 4 first tokens kept), heads of the linear attention
+# (128 x 128 state a head), 8 experts of which 2 run plus a shared expert.  The Qwen3 model beside each has the
+# same width, layers and heads and an intermediate size of what a Dobepel token runs through (2 experts + shared).
+DOBEPEL_SIZES = {
+    "1k": dict(width=1024, layers=4, heads=8, kv_heads=2, lin_heads=8, expert_ff=512, shared_ff=512),
+    "2k": dict(width=2048, layers=4, heads=16, kv_heads=4, lin_heads=16, expert_ff=1024, shared_ff=1024),
+    "4k": dict(width=4096, layers=2, heads=32, kv_heads=8, lin_heads=32, expert_ff=2048, shared_ff=2048),
+}
+DOBEPEL_VOCAB, DOBEPEL_WINDOW, DOBEPEL_KEEP, DOBEPEL_EXPERTS, DOBEPEL_TOP = 32000, 1024, 4, 8, 2
+
+
+def dobepel_raw(sz):
+    left = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "mask": {"size": DOBEPEL_WINDOW, "keep_first": DOBEPEL_KEEP}}
+    right = {"heads": sz["lin_heads"], "dim": 128, "vdim": 128,
+             "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, sz["lin_heads"] - 1)) for h in range(sz["lin_heads"])]}
+    mlp = {"kind": "moe", "expert": {"ff": sz["expert_ff"]}, "router": {"experts": DOBEPEL_EXPERTS, "top": DOBEPEL_TOP},
+           "shared": {"ff": sz["shared_ff"]}}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp}
+    return {"architecture": "Dobepel", "vocab": DOBEPEL_VOCAB, "width": sz["width"], "residual_mult": 0.5, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 8191}},
+            "layers": [json.loads(json.dumps(layer)) for _ in range(sz["layers"])]}
+
+
+def qwen_raw_like(sz):
+    return dict(MODEL, vocab_size=DOBEPEL_VOCAB, hidden_size=sz["width"], num_hidden_layers=sz["layers"],
+                num_attention_heads=sz["heads"], num_key_value_heads=sz["kv_heads"], head_dim=128,
+                intermediate_size=DOBEPEL_TOP * sz["expert_ff"] + sz["shared_ff"], tie_word_embeddings=False)
+
+
+def dobepel_workload(args, pk):
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at 2,048 cached tokens) of Dobepel
+    and of Qwen3 at equal size, through the step function, timed with CUDA events; then the design's own kernels
+    beside the like kernels of Qwen3 at the 2k size, each as a fraction of its roofline."""
+    import torch
+    from velox_b200 import Engine, EngineConfig
+    from velox_b200.config import DobepelConfig, Qwen3Config
+    from velox_b200.csrc import ops
+    from velox_b200.engine import StepEntry
+
+    T, B, CTX = 2048, 8, 2048
+    K, W = max(1, min(args.steps, 32)), max(3, args.warmup)
+    gen = torch.Generator().manual_seed(SEED)
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    def model_points(cfg, vocab):
+        eng = Engine(model_config=cfg, random_seed=SEED, config=EngineConfig(
+            dtype="bfloat16", page_size=PAGE, num_pages=(B + 1) * ((CTX + 64) // PAGE + 1), max_running_requests=B + 1,
+            max_batch_tokens=T, max_model_len=CTX + 64))
+        toks = torch.randint(0, vocab, (B + 1, CTX), generator=gen).tolist()
+
+        def prefill():
+            eng.cache.add_request("p")
+            eng.run_step([StepEntry("p", toks[B][:T], [T - 1])])
+            eng.cache.release("p")
+        for _ in range(3):
+            prefill()
+        pms = timed(prefill, 5)
+        for i in range(B):
+            eng.cache.add_request(i)
+            eng.run_step([StepEntry(i, toks[i][:CTX - K - W - 2], [])])
+        entries = [StepEntry(i, [toks[i][-1]], [0]) for i in range(B)]
+        zeros, ones = [0.0] * B, [1.0] * B
+
+        def step():
+            eng.runner.step_and_sample(entries, zeros, ones, zeros)
+        for _ in range(W):
+            step()
+        n0 = ops.launch_count()
+        dms = timed(step, K)
+        launches = (ops.launch_count() - n0) // K
+        ops.check_device_errors()
+        del eng
+        torch.cuda.empty_cache()
+        return {"prefill_ms": round(pms, 3), "prefill_tok_s": round(T * 1000.0 / pms, 1), "decode_ms_per_step": round(dms, 4),
+                "decode_tok_s": round(B * 1000.0 / dms, 1), "launches_per_decode_step": int(launches)}
+
+    sizes = {}
+    for name, sz in DOBEPEL_SIZES.items():
+        sizes[name] = {"dobepel": model_points(DobepelConfig.from_dict(dobepel_raw(sz)), DOBEPEL_VOCAB),
+                       "qwen3": model_points(Qwen3Config.from_dict(qwen_raw_like(sz)), DOBEPEL_VOCAB), "shape": sz}
+    out = {"metric": "Dobepel beside Qwen3 at equal size: prefill of %d tokens, decode at batch %d with %d cached tokens, bf16"
+                     % (T, B, CTX), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "sizes": sizes,
+           "value": sizes["2k"]["dobepel"]["decode_tok_s"], "higher_is_better": True,
+           "kernels": dobepel_kernels(pk, DOBEPEL_SIZES["2k"], timed), "peaks": pk,
+           "data": "synthetic: random weights N(0,0.02) seed 2, uniform random token ids; inputs of the kernel rows rotate "
+                   "through buffers larger than L2 where they are bound by memory"}
+    return out
+
+
+def dobepel_kernels(pk, sz, timed):
+    """Microseconds and fractions of the roofline of Dobepel's kernels and of Qwen3's like kernels at one size."""
+    import torch
+    from velox_b200.csrc import ops
+    dev, bf = "cuda:0", torch.bfloat16
+    E, H, G, HL, D = sz["width"], sz["heads"], sz["kv_heads"], sz["lin_heads"], 128
+    T, B, CTX, S, win, keep = 2048, 8, 2048, PAGE, DOBEPEL_WINDOW, DOBEPEL_KEEP
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = {}
+
+    def row(name, us, flops=0.0, nbytes=0.0):
+        t = us * 1e-6
+        frac_c, frac_m = flops / t / tf, nbytes / t / hbm
+        rows[name] = {"us": round(us, 2), "bound": "tensor" if frac_c >= frac_m else "hbm",
+                      "frac": round(max(frac_c, frac_m), 4)}
+
+    def us(fn, n=20):
+        """Microseconds a call of `fn`: n calls recorded in one CUDA graph (so that the host's share of a launch
+        does not count), replayed three times for warm-up and five times under CUDA events."""
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(n):
+                fn()
+        for _ in range(3):
+            g.replay()
+        return timed(g.replay, 5) * 1000.0 / n
+    ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    pages = B * (CTX // S)
+    kp = torch.randn((pages, G, S, D), device=dev).to(bf)
+    vp = torch.randn((pages, G, S, D), device=dev).to(bf)
+    bt = torch.arange(pages, dtype=torch.int32, device=dev).view(B, CTX // S)
+    # -- attention over a prompt of T tokens (one request), window 1,024 --
+    q = torch.randn((T, (H + 2 * G) * D), device=dev).to(bf)
+    cu, off = ints([0, T]), ints([0])
+    vis = sum(min(i + 1, win) + (min(keep, i + 1 - win) if i + 1 > win else 0) for i in range(T))
+    fl = 2.0 * vis * 2 * D * H
+    row("prompt attention, biased window (mma.sync, P in two halves)",
+        us(lambda: ops.biased_prefill_attention(q, q.shape[1], kp, vp, bt, cu, off, D ** -0.5, win, keep, 8.0, H, G, D, D, 1, T, T)), fl)
+    row("prompt attention, Qwen3 (mma.sync)",
+        us(lambda: ops.paged_prefill_attention(q, q.shape[1], kp, vp, bt, cu, off, D ** -0.5, win, H, G, D, 1, T, T)), fl)
+    row("prompt attention, Qwen3 (tcgen05)",
+        us(lambda: ops.paged_prefill_attention_tc(q, q.shape[1], kp, vp, bt, cu, off, D ** -0.5, win, H, G, D, 1, T, T)), fl)
+    # -- attention of B single tokens at CTX cached tokens --
+    qd = torch.randn((B, (H + 2 * G) * D), device=dev).to(bf)
+    seqs, pos = ints(list(range(B))), ints([CTX - 1] * B)
+    nb = B * G * (win + keep) * 2 * D * 2.0
+    row("decode attention, biased window", us(lambda: ops.biased_decode_attention(
+        qd, qd.shape[1], kp, vp, bt, seqs, pos, D ** -0.5, win, keep, 8.0, H, G, D, D, B), 50), 0.0, nb)
+    row("decode attention, Qwen3", us(lambda: ops.paged_decode_attention(
+        qd, qd.shape[1], kp, vp, bt, seqs, pos, D ** -0.5, win, H, G, D, B, CTX), 50), 0.0, B * G * win * 2 * D * 2.0)
+    # -- linear attention --
+    x = (torch.randn((T, 4 * HL * D), device=dev) * 0.5).to(bf)
+    decay = torch.full((HL,), 0.97, device=dev)
+    state = torch.zeros((B, HL, D, D), device=dev)
+    lin_fl = T * HL * 2.0 * (32 * 2 * D + 2 * D * D)   # scores and values within chunks of 64 (half of them), state read and update
+    slot0, cu_b, slots_b = ints([0]), ints(list(range(B + 1))), ints(list(range(B)))
+    row("prompt linear attention, chunked (mma.sync, halves)", us(lambda: ops.linear_attention(
+        x, 0, HL * D, 2 * HL * D, decay, state, cu, slot0, 1, T, HL, D, D)), lin_fl)
+    xd = (torch.randn((B, 4 * HL * D), device=dev) * 0.5).to(bf)
+    row("decode linear attention, recurrent", us(lambda: ops.linear_attention(
+        xd, 0, HL * D, 2 * HL * D, decay, state, cu_b, slots_b, B, 1, HL, D, D), 50),
+        0.0, B * HL * D * D * 4 * 2.0)
+    # -- feed-forward: routed experts against the dense gated product --
+    NE, top, F = DOBEPEL_EXPERTS, DOBEPEL_TOP, sz["expert_ff"]
+    h = torch.randn((T, E), device=dev).to(bf)
+    wr, gu = torch.randn((NE, E), device=dev) * 0.1, (torch.randn((NE, 2 * F, E), device=dev) * 0.02).to(bf)
+    dn = (torch.randn((NE, E, F), device=dev) * 0.02).to(bf)
+    plan = ops.moe_route(h, wr, None, NE, top)
+    a = ops.moe_gemm(h, gu, plan, True, bf, gated_activation="silu")
+    row("experts gate_up, %d rows (grouped mma.sync)" % (T * top), us(lambda: ops.moe_gemm(h, gu, plan, True, bf, gated_activation="silu")),
+        2.0 * T * top * 2 * F * E)
+    row("experts down, %d rows (grouped mma.sync)" % (T * top), us(lambda: ops.moe_gemm(a, dn, plan, False, torch.float32)),
+        2.0 * T * top * F * E)
+    row("router and plan, %d tokens" % T, us(lambda: ops.moe_route(h, wr, None, NE, top)), 0.0, T * E * 2.0)
+    I = top * F + sz["shared_ff"]
+    wq = (torch.randn((2 * I, E), device=dev) * 0.02).to(bf)
+    row("Qwen3 gate_up, %d rows (tcgen05, fused activation)" % T, us(lambda: ops.gemm_tcgen05(
+        h, wq, None, gated_activation="silu", pair=ops.tcgen05_pair_better(T, 2 * I, h.device))), 2.0 * T * 2 * I * E)
+    hd = torch.randn((B, E), device=dev).to(bf)
+    pland = ops.moe_route(hd, wr, None, NE, top)
+    many = [(torch.randn((NE, 2 * F, E), device=dev) * 0.02).to(bf) for _ in range(max(2, int(3e8 // (NE * 2 * F * E * 2))))]
+    k = [0]
+
+    def experts_decode():
+        k[0] = (k[0] + 1) % len(many)
+        ops.moe_gemm(hd, many[k[0]], pland, True, bf, gated_activation="silu")
+    touched = min(NE, B * top)
+    row("experts gate_up, %d tokens (decode)" % B, us(experts_decode, 50), 0.0, touched * 2 * F * E * 2.0)
+    manyq = [(torch.randn((2 * I, E), device=dev) * 0.02).to(bf) for _ in range(max(2, int(3e8 // (2 * I * E * 2))))]
+
+    def dense_decode():
+        k[0] = (k[0] + 1) % len(manyq)
+        ops.gemm_skinny(hd, manyq[k[0]], None, bf, gated_activation="silu")
+    row("Qwen3 gate_up, %d tokens (decode, skinny)" % B, us(dense_decode, 50), 0.0, 2 * I * E * 2.0)
+    # -- norms and residual --
+    big = 16384   # rows: float32 residual + two branches, far larger than L2
+    res = torch.randn((big, E), device=dev)
+    y0, y1 = torch.randn((big, E), device=dev).to(bf), torch.randn((big, E), device=dev).to(bf)
+    w = torch.ones(E, device=dev)
+    row("two branch norms + sum + norm + residual + next norm, %d rows" % big,
+        us(lambda: ops.merge_norm_add_norm(res, y0, w, 0.5, 1e-6, w, 0.5, y1, w, 0.5, w_next=w), 10), 0.0, big * E * (4 + 4 + 2 + 2 + 2.0))
+    row("Qwen3 residual add + norm, %d rows" % big, us(lambda: ops.add_rmsnorm(res, y0, w, 1e-6, bf), 10), 0.0, big * E * (4 + 4 + 2 + 2.0))
+    return rows
+
+
 def main() -> int:
     global CONTEXT, PROMPT
     ap = argparse.ArgumentParser()
@@ -202,10 +411,11 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (recorded in config)")
     ap.add_argument("--batch", type=int, default=BATCH)
-    ap.add_argument("--workload", default="decode", choices=["decode", "stream"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "dobepel"],
                     help="decode: the benchmark (steady decoding at a fixed batch). stream: continuous batching "
                          "under arrivals (64 requests, prompts of 128-4,096 tokens, 256 new tokens each, Poisson "
-                         "arrivals); prints its own JSON line")
+                         "arrivals); prints its own JSON line. dobepel: the Dobepel design beside Qwen3 at equal size "
+                         "(prefill, decode, and the design's kernels against their rooflines); its own JSON line")
     ap.add_argument("--arrival-rate", type=float, default=16.0, help="stream: mean arrivals a second")
     ap.add_argument("--lazy-graphs", action="store_true",
                     help="stream: capture each decode graph when a step first needs it, inside the run")
@@ -236,6 +446,12 @@ def main() -> int:
     from velox_b200.csrc import ops
     from velox_b200.engine import StepEntry
 
+    if args.workload == "dobepel":
+        with ClockSampler() as clocks:
+            res = dobepel_workload(args, peaks())
+        res["clocks"] = clocks.summary()
+        print(json.dumps(res))
+        return 0
     model = dict(MODEL, **SHAPES[args.shape])
     layers = args.layers or model["num_hidden_layers"]
     raw = dict(model, num_hidden_layers=layers)

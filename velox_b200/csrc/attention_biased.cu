@@ -5,9 +5,9 @@
 //   query i sees key j  iff  j <= i and (window == 0 or i - j < window or j < keep_first)
 //   keys of size DK (64, 128), values of size DV (32, 64, 128), which need not be equal
 //
-// grid (query tile, head, segment); 4 warps.  A segment is a request's portion of this step
-// (rows cu_seqlens[s] .. of positions kv_offsets[s] ..), or, for a step of single tokens, one
-// token row with its own position.  A block takes 64 query rows: 64 / G consecutive tokens
+// Portions: grid (query tile, head, segment); 4 warps.  A segment is a request's portion of this step
+// (rows cu_seqlens[s] .. of positions kv_offsets[s] ..).  A step of single tokens has a kernel of its
+// own further down, which deals one query's keys to the warps of a block.  A block takes 64 query rows: 64 / G consecutive tokens
 // times the G query heads of one kv head when G is a power of two up to 16 (they share every
 // key/value tile), else 64 tokens of one head; 16 rows per warp, held in registers as A
 // operands.  It walks the tiles of 64 keys that hold kept first positions before the window,
@@ -19,8 +19,8 @@
 //
 // A key slot that the mask hides is never read from a page that may have been given back: its
 // address is clamped to the nearest visible key.  The order of every sum depends only on the
-// query's own position and the request's keys, so a token's result is the same bits in a prompt's
-// portion, alone, or beside other requests.
+// query's own position and the request's keys, so a token's result does not depend on what else is in
+// the step (a token decoded alone and the same token inside a portion differ by rounding: other kernels).
 #include "common.cuh"
 #include "mma_helpers.cuh"
 
@@ -267,6 +267,219 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
     }
 }
 
+// ---- single tokens: the keys of one query dealt to the warps of a block ----
+// grid (kv head, or head when the group is no power of two up to 16; token row); 8 warps.  The visible keys of
+// a token (the kept first ones, then the window's) are numbered 0 .. n-1 and taken 16 at a time; group g goes to
+// warp g mod 8, which gathers its keys and values itself (cp.async, two stages of its own, no block barrier),
+// forms the scores of the group's query heads (rows of one m16 tile) and keeps a running maximum, sum and
+// output of its own.  At the end the warps' parts are added in warp order.
+#define AD_WARPS 8
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(AD_WARPS * 32)
+biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ k_pool,
+                     const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
+                     const int* __restrict__ seq_of_token, const int* __restrict__ positions, bf16* __restrict__ out,
+                     int out_row_stride, float scale_log2, float bias_exp, int window, int keep_first, int H, int Hk,
+                     int S, int share_log2) {
+    extern __shared__ __align__(128) unsigned char ad_smem[];
+    constexpr int KCH = DK / 8, VCH = DV / 8;
+    constexpr int K_BYTES = 16 * DK * 2, V_BYTES = 16 * DV * 2;
+    constexpr int WARP_BYTES = 2 * (K_BYTES + V_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.y;
+    const int share = 1 << share_log2;
+    const int hk = share > 1 ? blockIdx.x : blockIdx.x / (H / Hk);
+    const int head0 = share > 1 ? hk * share : blockIdx.x;
+    unsigned char* q_s = ad_smem;                                  // [16][DK]
+    unsigned char* mine = ad_smem + 16 * DK * 2 + warp * WARP_BYTES;
+    float* part = reinterpret_cast<float*>(ad_smem + 16 * DK * 2); // after the walk: [warp][16 rows][DV + 2]
+    pdl_wait();
+    pdl_trigger();
+    const int pos = positions[t];
+    const int* bt = block_table + (size_t)seq_of_token[t] * max_blocks;
+    const int kv_len = pos + 1;
+    const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    const int nkept = window > 0 ? min(keep_first, start) : 0;
+    const int nkeys = nkept + kv_len - start;
+    const int ngroups = (nkeys + 15) >> 4;
+
+    for (int c = threadIdx.x; c < 16 * KCH; c += AD_WARPS * 32) {
+        const int r = c / KCH, cc = c % KCH;
+        const int hd = head0 + min(r, share - 1);   // rows past the group repeat its last head
+        *reinterpret_cast<uint4*>(q_s + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4)) =
+            *reinterpret_cast<const uint4*>(q + (size_t)t * q_row_stride + (size_t)hd * DK + cc * 8);
+    }
+    auto issue = [&](int g, int stage) {
+        unsigned char* ks = mine + stage * (K_BYTES + V_BYTES);
+        unsigned char* vs = ks + K_BYTES;
+        for (int c = lane; c < 16 * KCH; c += 32) {
+            const int r = c / KCH, cc = c % KCH;
+            const int n = min(g * 16 + r, nkeys - 1);
+            const int key = n < nkept ? n : start + n - nkept;
+            const int page = bt[key / S];
+            cp_async16(ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4),
+                       k_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DK + cc * 8);
+        }
+        for (int c = lane; c < 16 * VCH; c += 32) {
+            const int r = c / VCH, cc = c % VCH;
+            const int n = min(g * 16 + r, nkeys - 1);
+            const int key = n < nkept ? n : start + n - nkept;
+            const int page = bt[key / S];
+            cp_async16(vs + r * (DV * 2) + (ab_swz<VCH>(r, cc) << 4),
+                       v_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DV + cc * 8);
+        }
+    };
+    if (warp < ngroups) issue(warp, 0);
+    cp_async_commit();
+    __syncthreads();   // the queries are in shared memory
+    const int mi = lane >> 3;
+    unsigned qf[DK / 16][4];
+    {
+        const int r = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk)
+            ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], q_s + r * (DK * 2) + (ab_swz<KCH>(r, 2 * kk + (mi >> 1)) << 4));
+    }
+    float o[DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int r0 = lane >> 2;
+    const int hd0 = head0 + min(r0, share - 1), hd1 = head0 + min(r0 + 8, share - 1);
+    const float sl[2] = {bias_exp > 0.f ? exp2f(-bias_exp * (float)(hd0 + 1) / (float)H) * AB_LOG2E : 0.f,
+                         bias_exp > 0.f ? exp2f(-bias_exp * (float)(hd1 + 1) / (float)H) * AB_LOG2E : 0.f};
+    int it = 0;
+    for (int g = warp; g < ngroups; g += AD_WARPS, ++it) {
+        const int stage = it & 1;
+        if (g + AD_WARPS < ngroups) issue(g + AD_WARPS, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const unsigned char* ks = mine + stage * (K_BYTES + V_BYTES);
+        const unsigned char* vs = ks + K_BYTES;
+        float sc[2][4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[0][c] = sc[1][c] = 0.f;
+        {
+            const int r = ((mi >> 1) << 3) + (lane & 7);
+#pragma unroll
+            for (int kk = 0; kk < DK / 16; ++kk) {
+                unsigned b00, b01, b10, b11;
+                ldmatrix_x4(b00, b01, b10, b11, ks + r * (DK * 2) + (ab_swz<KCH>(r, 2 * kk + (mi & 1)) << 4));
+                mma_bf16(sc[0], qf[kk], b00, b01);
+                mma_bf16(sc[1], qf[kk], b10, b11);
+            }
+        }
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int n = g * 16 + nt * 8 + ((lane & 3) << 1) + c;
+                    const int key = n < nkept ? n : start + n - nkept;
+                    float& v = sc[nt][2 * hrow + c];
+                    v = n < nkeys ? v * scale_log2 - sl[hrow] * (float)(pos - key) : -INFINITY;
+                    mx = fmaxf(mx, v);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m[hrow], mx);   // (a group has at least one visible key: never -inf)
+            const float alpha = exp2f(m[hrow] - m_new);
+            float ps = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    float& v = sc[nt][2 * hrow + c];
+                    v = exp2f(v - m_new);
+                    ps += v;
+                }
+            l[hrow] = l[hrow] * alpha + ps;
+            m[hrow] = m_new;
+#pragma unroll
+            for (int i2 = 0; i2 < DV / 8; ++i2) {
+                o[i2][2 * hrow] *= alpha;
+                o[i2][2 * hrow + 1] *= alpha;
+            }
+        }
+        unsigned hi[4], lw[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const float a = sc[x >> 1][2 * (x & 1)], b = sc[x >> 1][2 * (x & 1) + 1];
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
+            const float2 back = __bfloat1622float2(h2);
+            hi[x] = *reinterpret_cast<const unsigned*>(&h2);
+            lw[x] = pack_bf16(a - back.x, b - back.y);
+        }
+        const int rv = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; nt += 2) {
+            unsigned v00, v01, v10, v11;
+            ldmatrix_x4_trans(v00, v01, v10, v11, vs + rv * (DV * 2) + (ab_swz<VCH>(rv, nt + (mi >> 1)) << 4));
+            mma_bf16(o[nt], hi, v00, v01);
+            mma_bf16(o[nt + 1], hi, v10, v11);
+            mma_bf16(o[nt], lw, v00, v01);
+            mma_bf16(o[nt + 1], lw, v10, v11);
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+    __syncthreads();   // every warp is done with its stages: the same memory now takes the warps' parts
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+        l[hrow] += __shfl_xor_sync(0xffffffffu, l[hrow], 1);
+        l[hrow] += __shfl_xor_sync(0xffffffffu, l[hrow], 2);
+        float* p = part + ((size_t)warp * 16 + r0 + 8 * hrow) * (DV + 2);
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt) {
+            p[nt * 8 + ((lane & 3) << 1)] = o[nt][2 * hrow];
+            p[nt * 8 + ((lane & 3) << 1) + 1] = o[nt][2 * hrow + 1];
+        }
+        if ((lane & 3) == 0) { p[DV] = m[hrow]; p[DV + 1] = l[hrow]; }
+    }
+    __syncthreads();
+    const int live = share;   // rows that are query heads
+    for (int e = threadIdx.x; e < live * DV; e += AD_WARPS * 32) {
+        const int r = e / DV, d = e - r * DV;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, part[((size_t)w * 16 + r) * (DV + 2) + DV]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) {
+            const float* p = part + ((size_t)w * 16 + r) * (DV + 2);
+            const float f = p[DV] == -INFINITY ? 0.f : exp2f(p[DV] - M);
+            L += p[DV + 1] * f;
+            acc += p[d] * f;
+        }
+        out[(size_t)t * out_row_stride + (size_t)(head0 + r) * DV + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+template <int DK, int DV>
+static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool,
+                                const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
+                                bf16* out, int out_row_stride, float scale, float bias_exp, int window, int keep_first,
+                                int tokens, int H, int Hk, int S, cudaStream_t stream) {
+    const size_t walk = (size_t)AD_WARPS * 2 * (16 * DK * 2 + 16 * DV * 2), parts = (size_t)AD_WARPS * 16 * (DV + 2) * 4;
+    const size_t smem = 16 * DK * 2 + (walk > parts ? walk : parts);
+    static bool configured[VX_MAX_DEVICES];
+    if (int rc = vx_configure_smem(biased_decode_kernel<DK, DV>, smem, configured)) return rc;
+    const int G = H / Hk;
+    int share_log2 = 0;
+    if (G > 1 && G <= 16 && (G & (G - 1)) == 0)
+        while ((1 << share_log2) < G) ++share_log2;
+    dim3 grid(share_log2 ? Hk : H, tokens);
+    VX_LAUNCH_K(VX_K_ATTENTION, (biased_decode_kernel<DK, DV>), grid, AD_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
+                v_pool, block_table, max_blocks, seq_of_token, positions, out, out_row_stride, scale * AB_LOG2E, bias_exp,
+                window, keep_first, H, Hk, S, share_log2);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
 template <int DK, int DV>
 static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
                          int max_blocks, AbSegments seg, bf16* out, int out_row_stride, float scale, float bias_exp,
@@ -299,6 +512,17 @@ extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* 
     if (cu_seqlens ? !kv_offsets : (!seq_of_token || !positions || max_new != 1)) return VX_ERR_SHAPE;
     if (H > 65535 || segments > 65535) return VX_ERR_LIMIT;
     if ((q_row_stride & 7) || (((uintptr_t)q) & 15) || (out_row_stride & 1) || (((uintptr_t)out) & 3)) return VX_ERR_ALIGN;
+    if (!cu_seqlens) {
+        if (segments > 65535) return VX_ERR_LIMIT;
+#define AD_GO(K_, V_)                                                                                                       \
+    if (DK == K_ && DV == V_)                                                                                               \
+        return launch_biased_decode<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,       \
+                                            block_table, max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, \
+                                            scale, bias_exp, window, keep_first, segments, H, Hk, S, stream)
+        AD_GO(64, 32); AD_GO(64, 64); AD_GO(64, 128); AD_GO(128, 32); AD_GO(128, 64); AD_GO(128, 128);
+#undef AD_GO
+        return VX_ERR_SHAPE;
+    }
     AbSegments seg = {cu_seqlens, kv_offsets, seq_of_token, positions};
 #define AB_GO(K_, V_)                                                                                                     \
     if (DK == K_ && DV == V_)                                                                                             \

@@ -19,11 +19,23 @@
 #define MOE_MAX_EXPERTS 256
 #define MOE_MAX_TOP 32
 
+__device__ __forceinline__ void route_load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void route_load8(const bf16* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+
+// `vec`: K a multiple of 8 and 16-byte aligned rows (the host checks); else element by element.
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_router, const float* __restrict__ bias,
                  int tokens, int K, int E, int top, int* __restrict__ chosen, float* __restrict__ weight,
-                 int* __restrict__ counts, int* __restrict__ pos) {
+                 int* __restrict__ counts, int* __restrict__ pos, int vec) {
     __shared__ float z_s[4][MOE_MAX_EXPERTS];
     __shared__ float zc_s[4][MOE_MAX_TOP];
     pdl_wait();
@@ -33,12 +45,42 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
     if (t >= tokens) return;
     const T* row = h + (size_t)t * ldh;
     float* z = z_s[warp];
-    for (int e = 0; e < E; ++e) {
-        const float* w = w_router + (size_t)e * K;
-        float s = 0.f;
-        for (int k = lane; k < K; k += 32) s = fmaf(to_f32(row[k]), w[k], s);
-        s = warp_sum(s);
-        if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+    if (vec) {
+        // eight experts at a time: a lane takes 8 consecutive k of the token's row (one 16-byte load for a bfloat16
+        // row) and the same 8 of each expert's row, so that 17 independent loads are in flight per step
+        for (int e0 = 0; e0 < E; e0 += 8) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int k = lane * 8; k < K; k += 256) {
+                float hv[8];
+                route_load8(row + k, hv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (e0 + j < E) {
+                        const float4 a = *reinterpret_cast<const float4*>(w_router + (size_t)(e0 + j) * K + k);
+                        const float4 b = *reinterpret_cast<const float4*>(w_router + (size_t)(e0 + j) * K + k + 4);
+                        acc[j] = fmaf(hv[0], a.x, acc[j]); acc[j] = fmaf(hv[1], a.y, acc[j]);
+                        acc[j] = fmaf(hv[2], a.z, acc[j]); acc[j] = fmaf(hv[3], a.w, acc[j]);
+                        acc[j] = fmaf(hv[4], b.x, acc[j]); acc[j] = fmaf(hv[5], b.y, acc[j]);
+                        acc[j] = fmaf(hv[6], b.z, acc[j]); acc[j] = fmaf(hv[7], b.w, acc[j]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float s = warp_sum(acc[j]);
+                if (lane == 0 && e0 + j < E) z[e0 + j] = s + (bias ? bias[e0 + j] : 0.f);
+            }
+        }
+    } else {
+        for (int e = 0; e < E; ++e) {
+            const float* w = w_router + (size_t)e * K;
+            float s = 0.f;
+            for (int k = lane; k < K; k += 32) s = fmaf(to_f32(row[k]), w[k], s);
+            s = warp_sum(s);
+            if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+        }
     }
     __syncwarp();
     for (int i = 0; i < top; ++i) {
@@ -113,12 +155,14 @@ extern "C" int vx_moe_route(const void* h, int ldh, const float* w_router, const
     if (K <= 0 || E <= 0 || top <= 0 || top > E || tile_rows <= 0) return VX_ERR_SHAPE;
     if (E > MOE_MAX_EXPERTS || top > MOE_MAX_TOP) return VX_ERR_LIMIT;
     const int blocks = (tokens + 3) / 4;
+    const int elt = dtype == VX_F32 ? 4 : 2;
+    const int vec = K % 8 == 0 && (ldh * elt) % 16 == 0 && !(((uintptr_t)h) & 15) && !(((uintptr_t)w_router) & 15);
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_route_kernel<float>), blocks, 128, 0, stream, (const float*)h, ldh, w_router, bias,
-                    tokens, K, E, top, chosen, weight, counts, pos);
+                    tokens, K, E, top, chosen, weight, counts, pos, vec);
     else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_route_kernel<bf16>), blocks, 128, 0, stream, (const bf16*)h, ldh, w_router, bias,
-                    tokens, K, E, top, chosen, weight, counts, pos);
+                    tokens, K, E, top, chosen, weight, counts, pos, vec);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_K(VX_K_ELEMENTWISE, moe_plan_kernel, 1, 1024, 0, stream, (const int*)chosen, (const int*)pos, counts,
@@ -204,20 +248,25 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ 
 
 // ---- grouped product on the tensor cores (bfloat16 operands, float32 accumulators) ----
 // A block of 4 warps owns a tile of 64 rows x 64 columns; warp w takes rows 32 * (w & 1) and
-// columns 32 * (w >> 1).  k runs in steps of 32 through two shared-memory stages filled by
-// 16-byte asynchronous copies (rows that do not exist are zero).  K a multiple of 8.
+// columns 32 * (w >> 1).  k runs in steps of 64 (128 bytes of every row) through three
+// shared-memory stages filled by 16-byte asynchronous copies, two of them in flight while one is
+// multiplied (rows that do not exist are zero).  K a multiple of 8.
 #define MT_BM 64
 #define MT_BN 64
-#define MT_BK 32
-#define MT_LD (MT_BK + 8)   // (a row of 80 bytes: the 8 rows of a matrix load miss each other's banks)
+#define MT_BK 64
+#define MT_STAGES 3
+#define MT_LD (MT_BK + 8)   // (a row of 144 bytes: the 8 rows of a matrix load miss each other's banks)
+#define MT_SMEM (MT_STAGES * (MT_BM + MT_BN) * MT_LD * 2)
 
 template <typename TC>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ src_of_row, int src_div,
                     const bf16* __restrict__ W, const int* __restrict__ tiles, const int* __restrict__ n_tiles,
                     TC* __restrict__ C, int ldc, int N, int K, int gated, int act) {
-    __shared__ __align__(16) bf16 As[2][MT_BM][MT_LD];
-    __shared__ __align__(16) bf16 Ws[2][MT_BN][MT_LD];
+    extern __shared__ __align__(16) unsigned char mt_smem[];
+    typedef bf16 (*Tile)[MT_BM][MT_LD];
+    Tile As = reinterpret_cast<Tile>(mt_smem);
+    Tile Ws = reinterpret_cast<Tile>(mt_smem + MT_STAGES * MT_BM * MT_LD * 2);
     __shared__ int src_s[MT_BM];
     pdl_wait();
     pdl_trigger();
@@ -241,11 +290,11 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
             for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
 
     auto load_stage = [&](int stage, int k0) {
-        // 64 rows x 4 chunks of 8 elements per operand; 128 threads take 2 chunks of each
+        // 64 rows x 8 chunks of 8 elements per operand; 128 threads take 4 chunks of each
 #pragma unroll
-        for (int it = 0; it < 2; ++it) {
+        for (int it = 0; it < 4; ++it) {
             const int idx = tid + it * 128;
-            const int r = idx >> 2, ck = (idx & 3) * 8;
+            const int r = idx >> 3, ck = (idx & 7) * 8;
             const int k = k0 + ck;
             bf16* da = &As[stage][r][ck];
             const int s = src_s[r];
@@ -261,11 +310,12 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
 
     const int nk = (K + MT_BK - 1) / MT_BK;
     load_stage(0, 0);
+    if (nk > 1) load_stage(1, MT_BK); else cp_async_commit();
     for (int kb = 0; kb < nk; ++kb) {
-        const int cur = kb & 1;
-        if (kb + 1 < nk) { load_stage(cur ^ 1, (kb + 1) * MT_BK); cp_async_wait<1>(); }
-        else cp_async_wait<0>();
-        __syncthreads();
+        const int cur = kb % MT_STAGES;
+        cp_async_wait<1>();   // all but the newest group have landed: stage `cur` is there
+        __syncthreads();      // ... for every thread's copies, and everybody is done with the stage filled next
+        if (kb + 2 < nk) load_stage((kb + 2) % MT_STAGES, (kb + 2) * MT_BK); else cp_async_commit();
 #pragma unroll
         for (int ks = 0; ks < MT_BK; ks += 16) {
             unsigned a[2][4], b[4][2];
@@ -284,7 +334,6 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
 #pragma unroll
                 for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], a[i], b[j][0], b[j][1]);
         }
-        __syncthreads();
     }
     // accumulator layout of m16n8: c0,c1 at (row lane/4, cols 2*(lane%4), +1); c2,c3 eight rows further down
 #pragma unroll
@@ -329,11 +378,14 @@ extern "C" int vx_moe_gemm(const void* A, int lda, const int* src_of_row, int sr
     if (tensor_cores) {
         if (in_dtype != VX_BF16) return VX_ERR_DTYPE;
         if (K % 8 || lda % 8 || (((uintptr_t)A) | ((uintptr_t)W)) & 15) return VX_ERR_ALIGN;
+        static bool configured_b[VX_MAX_DEVICES], configured_f[VX_MAX_DEVICES];
+        if (int rc = out_dtype == VX_BF16 ? vx_configure_smem(moe_gemm_mma_kernel<bf16>, MT_SMEM, configured_b)
+                                          : vx_configure_smem(moe_gemm_mma_kernel<float>, MT_SMEM, configured_f)) return rc;
         if (out_dtype == VX_BF16)
-            VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_mma_kernel<bf16>), grid, 128, 0, stream, (const bf16*)A, lda, src_of_row, src_div,
+            VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_mma_kernel<bf16>), grid, 128, MT_SMEM, stream, (const bf16*)A, lda, src_of_row, src_div,
                         (const bf16*)W, tiles, n_tiles, (bf16*)C, ldc, N, K, gated, act);
         else if (out_dtype == VX_F32)
-            VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_mma_kernel<float>), grid, 128, 0, stream, (const bf16*)A, lda, src_of_row, src_div,
+            VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_mma_kernel<float>), grid, 128, MT_SMEM, stream, (const bf16*)A, lda, src_of_row, src_div,
                         (const bf16*)W, tiles, n_tiles, (float*)C, ldc, N, K, gated, act);
         else
             return VX_ERR_DTYPE;

@@ -131,6 +131,165 @@ __global__ void merge_norm_add_norm_kernel(float* __restrict__ residual, const T
     for (int i = threadIdx.x; i < width; i += blockDim.x) out[base + i] = from_f32<T>(row[i] * rr * w_next[i]);
 }
 
+// The same with 8 elements per thread and access and the row in registers (width a multiple of 8, at most
+// 8 * 256 * 4, 16-byte aligned pointers).
+#define MN_THREADS 256
+
+__device__ __forceinline__ void mn_load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void mn_load8(const bf16* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void mn_store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void mn_store8(bf16* p, const float (&v)[8]) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+}
+
+template <typename T, int ITER>
+__global__ void __launch_bounds__(MN_THREADS)
+merge_norm_add_norm_vec_kernel(float* __restrict__ residual, const T* __restrict__ y0, const float* __restrict__ w0,
+                               float c0, const T* __restrict__ y1, const float* __restrict__ w1, float c1,
+                               const float* __restrict__ w_post, float mult, const float* __restrict__ w_next,
+                               T* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[32];
+    const int chunks = width >> 3;
+    const size_t base = (size_t)blockIdx.x * width;
+    const float inv = 1.f / (float)width;
+    // the residual is older than the branches (they were computed from it): it is asked for before the wait
+    float r[ITER][8];
+    if (w_post) {
+#pragma unroll
+        for (int i = 0; i < ITER; ++i) {
+            const int c = threadIdx.x + i * MN_THREADS;
+            if (c < chunks) mn_load8(residual + base + c * 8, r[i]);
+        }
+    }
+    pdl_wait();
+    pdl_trigger();
+    float u[ITER][8];
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = threadIdx.x + i * MN_THREADS;
+        if (c < chunks) {
+            mn_load8(y0 + base + c * 8, u[i]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s0 += u[i][j] * u[i][j];
+        }
+    }
+    float su = s0;
+    if (w0) {
+        s0 = block_sum(s0, scratch);
+        const float r0 = c0 * rsqrtf(s0 * inv + eps);
+        float b[ITER][8];
+        if (y1) {
+#pragma unroll
+            for (int i = 0; i < ITER; ++i) {
+                const int c = threadIdx.x + i * MN_THREADS;
+                if (c < chunks) {
+                    mn_load8(y1 + base + c * 8, b[i]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) s1 += b[i][j] * b[i][j];
+                }
+            }
+            s1 = block_sum(s1, scratch);
+        }
+        const float r1 = y1 ? c1 * rsqrtf(s1 * inv + eps) : 0.f;
+        su = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITER; ++i) {
+            const int c = threadIdx.x + i * MN_THREADS;
+            if (c < chunks) {
+                float wa[8], wb[8];
+                mn_load8(w0 + c * 8, wa);
+                if (y1) mn_load8(w1 + c * 8, wb);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float v = u[i][j] * r0 * wa[j];
+                    if (y1) v += b[i][j] * r1 * wb[j];
+                    u[i][j] = v;
+                    su += v * v;
+                }
+            }
+        }
+    }
+    if (!w_post) {
+#pragma unroll
+        for (int i = 0; i < ITER; ++i) {
+            const int c = threadIdx.x + i * MN_THREADS;
+            if (c < chunks) mn_store8(out + base + c * 8, u[i]);
+        }
+        return;
+    }
+    su = block_sum(su, scratch);
+    const float ru = mult * rsqrtf(su * inv + eps);
+    float sr = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = threadIdx.x + i * MN_THREADS;
+        if (c < chunks) {
+            float wp[8];
+            mn_load8(w_post + c * 8, wp);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                r[i][j] += u[i][j] * ru * wp[j];
+                sr += r[i][j] * r[i][j];
+            }
+            mn_store8(residual + base + c * 8, r[i]);
+        }
+    }
+    if (!w_next) return;
+    sr = block_sum(sr, scratch);
+    const float rr = rsqrtf(sr * inv + eps);
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = threadIdx.x + i * MN_THREADS;
+        if (c < chunks) {
+            float wn[8], y[8];
+            mn_load8(w_next + c * 8, wn);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = r[i][j] * rr * wn[j];
+            mn_store8(out + base + c * 8, y);
+        }
+    }
+}
+
+template <typename T>
+static int launch_merge_norm(float* residual, const T* y0, const float* w0, float c0, const T* y1, const float* w1, float c1,
+                             const float* w_post, float mult, const float* w_next, T* out, int rows, int width, float eps,
+                             cudaStream_t stream) {
+    const bool aligned = !((((uintptr_t)residual) | ((uintptr_t)y0) | ((uintptr_t)y1) | ((uintptr_t)w0) | ((uintptr_t)w1) |
+                            ((uintptr_t)w_post) | ((uintptr_t)w_next) | ((uintptr_t)out)) & 15);
+    if (width % 8 == 0 && aligned && width <= 8 * MN_THREADS * 4) {
+        const int iter = (width / 8 + MN_THREADS - 1) / MN_THREADS;
+#define MN_GO(I)                                                                                                      \
+    VX_LAUNCH_K(VX_K_ELEMENTWISE, (merge_norm_add_norm_vec_kernel<T, I>), rows, MN_THREADS, 0, stream, residual, y0, w0, \
+                c0, y1, w1, c1, w_post, mult, w_next, out, width, eps)
+        if (iter <= 1) MN_GO(1);
+        else if (iter == 2) MN_GO(2);
+        else MN_GO(4);
+#undef MN_GO
+    } else {
+        const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (merge_norm_add_norm_kernel<T>), rows, threads, sizeof(float) * width, stream, residual,
+                    y0, w0, c0, y1, w1, c1, w_post, mult, w_next, out, width, eps);
+    }
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
 extern "C" int vx_merge_norm_add_norm(float* residual, const void* y0, const float* w0, float c0, const void* y1,
                                       const float* w1, float c1, const float* w_post, float mult, const float* w_next,
                                       void* out, int rows, int width, float eps, int dtype, cudaStream_t stream) {
@@ -138,18 +297,13 @@ extern "C" int vx_merge_norm_add_norm(float* residual, const void* y0, const flo
     if (width <= 0 || !y0 || (y1 && (!w0 || !w1)) || (w_next && !out)) return VX_ERR_SHAPE;
     if (w_post ? !residual : (!out || !w0)) return VX_ERR_SHAPE;
     if (width > 12288) return VX_ERR_LIMIT;   // (the row lives in shared memory)
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    const size_t smem = sizeof(float) * width;
     if (dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (merge_norm_add_norm_kernel<float>), rows, threads, smem, stream, residual,
-                    (const float*)y0, w0, c0, (const float*)y1, w1, c1, w_post, mult, w_next, (float*)out, width, eps);
-    else if (dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (merge_norm_add_norm_kernel<bf16>), rows, threads, smem, stream, residual,
-                    (const bf16*)y0, w0, c0, (const bf16*)y1, w1, c1, w_post, mult, w_next, (bf16*)out, width, eps);
-    else
-        return VX_ERR_DTYPE;
-    VX_LAUNCH_CHECK();
-    return VX_OK;
+        return launch_merge_norm<float>(residual, (const float*)y0, w0, c0, (const float*)y1, w1, c1, w_post, mult, w_next,
+                                        (float*)out, rows, width, eps, stream);
+    if (dtype == VX_BF16)
+        return launch_merge_norm<bf16>(residual, (const bf16*)y0, w0, c0, (const bf16*)y1, w1, c1, w_post, mult, w_next,
+                                       (bf16*)out, rows, width, eps, stream);
+    return VX_ERR_DTYPE;
 }
 
 // out = act(x), element by element; x [rows, width] with a row stride, out contiguous.

@@ -171,8 +171,7 @@ class PagedAttention(Mixer):
     def _attend_extended(self, qkv, ctx, cache, group) -> torch.Tensor:
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
         if ops.biased_attention_supported(qkv.dtype, D, self.v_head_dim, cache.k_pool.shape[2]):
-            # the same kernel for portions and for single tokens (a step of single tokens hands it every row with its
-            # own position): a token's result is the same bits however its request was cut into steps
+            # a step of single tokens: every row with its own position, its keys dealt to the warps of a block
             if ctx.decode_only:
                 return ops.biased_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                                    ctx.seq_of_token, ctx.positions, self.scale, self.window,
