@@ -260,3 +260,35 @@ def test_router_grouped_products_and_combination(dtype, E, top, K, F, shared):
     # a second call on the same stream starts from clean counters
     plan2 = ops.moe_route(dev(h, dtype), dev(wr), dev(b), E, top)
     assert sorted(plan2.row_of.cpu().numpy().tolist()) == list(range(T * top))
+
+
+@pytest.mark.parametrize("E,top,K,F,T", [(8, 2, 128, 64, 700), (4, 3, 256, 136, 400), (16, 1, 64, 8, 1500)])
+def test_grouped_products_on_the_tcgen05_tensor_cores(E, top, K, F, T):
+    """Enough assignments for row tiles of 128: the tokens' rows copied into expert order, both grouped products by
+    the tcgen05 kernel (experts with no token, experts whose rows end inside a tile, a last column tile that ends
+    inside the next expert's matrix), the combination from bfloat16 rows."""
+    from velox_b200.csrc import ops
+    rng = np.random.default_rng(T)
+    h = bf(rng.normal(size=(T, K)))
+    wr, b = bf(rng.normal(size=(E, K)) * 0.5), bf(rng.normal(size=E))
+    b[E - 1] = -1e4   # the last expert never gets a token
+    w = {"router": wr, "router.b": b}
+    for e in range(E):
+        w.update({"e%d.gate" % e: bf(rng.normal(size=(F, K)) / 6), "e%d.up" % e: bf(rng.normal(size=(F, K)) / 6),
+                  "e%d.down" % e: bf(rng.normal(size=(K, F)) / 4)})
+    want = D.routed_ff(h, w, "", {"router": {"experts": E, "top": top}, "shared": None}, store=bf)
+    exact = D.routed_ff(h, w, "", {"router": {"experts": E, "top": top}, "shared": None})
+    gu = np.stack([np.concatenate([w["e%d.gate" % e].reshape(-1, 8, K), w["e%d.up" % e].reshape(-1, 8, K)], 1).reshape(2 * F, K)
+                   for e in range(E)])
+    down = np.stack([w["e%d.down" % e] for e in range(E)])
+    hd = dev(h, torch.bfloat16)
+    assert ops.moe_tcgen05_supported(hd, T * top, 2 * F, K)
+    plan = ops.moe_route(hd, dev(wr), dev(b), E, top, ops.MOE_TCGEN05_TILE_ROWS)
+    a = ops.moe_gemm_tcgen05(ops.moe_gather_rows(hd, plan), dev(gu, torch.bfloat16), plan, gated_activation="silu")
+    y = ops.moe_gemm_tcgen05(a, dev(down, torch.bfloat16), plan)
+    got = ops.moe_combine(y, plan, None, torch.bfloat16)
+    ops.check_device_errors()
+    close(got, exact, 2e-2)
+    # as far from the exact result as the plain implementation with the same roundings, give or take
+    g = got.float().cpu().numpy().astype(np.float64)
+    assert np.sqrt(np.mean((g - exact) ** 2)) <= 1.3 * np.sqrt(np.mean((want - exact) ** 2)) + 1e-6

@@ -32,13 +32,17 @@
 // and the block frees its tensor memory and returns.
 //
 // Sizes: K a multiple of 8, rows of A, W and C 16-byte aligned, N a multiple of 16.
+//
+// Grouped products (a routed feed-forward): with a list of row tiles (group, first row, rows; their number
+// on the device), tile t's rows are A[first row ..] (rows past the tile's own are read and not stored) and its
+// weights are W[group * N + column ..], W being all groups' matrices one after the other; see `csrc/moe.cu`.
 #include "tcgen05_gemm.cuh"
 
 template <int BN, int STAGES, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, bf16* __restrict__ C, int M, int N, int K, int ldc, int act,
-                    int* __restrict__ error) {
+                    int* __restrict__ error, const int* __restrict__ row_tiles, const int* __restrict__ n_row_tiles) {
     extern __shared__ unsigned char tc_smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ unsigned tmem_base_s;
@@ -53,7 +57,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // Tiles are numbered with the row tile running fastest, so that blocks working
     // at the same time share a tile of W and walk over the rows of A (which stays
     // in L2): W is read from memory once.  Block b takes tiles b, b + grid, ...
-    const int mtiles = (M + TC_BM - 1) / TC_BM, ntiles = (N + BN - 1) / BN;
+    const int mtiles = row_tiles ? n_row_tiles[0] : (M + TC_BM - 1) / TC_BM, ntiles = (N + BN - 1) / BN;
     const int total_tiles = mtiles * ntiles;
     const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
@@ -85,7 +89,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int it = 0;
             for (int ti = 0; ti < my_tiles && !failed; ++ti) {
                 const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
-                const int m0 = (tile % mtiles) * TC_BM, n0 = (tile / mtiles) * BN;
+                const int rt = tile % mtiles;
+                const int m0 = row_tiles ? row_tiles[3 * rt + 1] : rt * TC_BM;
+                const int n0 = (tile / mtiles) * BN + (row_tiles ? row_tiles[3 * rt] * N : 0);   // (row of W)
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES &&
@@ -147,8 +153,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int ti = 0; ti < my_tiles; ++ti) {
             const int buf = ti & 1;
             const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
-            const int m0 = (tile % mtiles) * TC_BM, n0 = (tile / mtiles) * BN;
-            const int row = m0 + quarter * 32 + lane;
+            const int rt = tile % mtiles;
+            const int m0 = row_tiles ? row_tiles[3 * rt + 1] : rt * TC_BM, n0 = (tile / mtiles) * BN;
+            // (a grouped tile stores only its own rows: those after them belong to the next group)
+            const int row = (row_tiles && quarter * 32 + lane >= row_tiles[3 * rt + 2]) ? M : m0 + quarter * 32 + lane;
             bool ok = tc_mbar_wait(tc_smem_u32(&acc_full[buf]), (unsigned)((ti >> 1) & 1));
             if (!ok && lane == 0) { failed = 1; atomicExch(error, TC_ERR_EPILOGUE); }
             ok = __all_sync(0xffffffffu, ok);
@@ -214,17 +222,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // ---- host side ----
 template <int BN, int STAGES, bool GATED>
 static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, bf16* C, int M, int N, int K,
-                     int ldc, int act, int* error, cudaStream_t stream) {
+                     int ldc, int act, int* error, cudaStream_t stream, const int* row_tiles = nullptr,
+                     const int* n_row_tiles = nullptr, int max_row_tiles = 0) {
     const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
     static bool configured[VX_MAX_DEVICES];
     if (int rc = vx_configure_smem(gemm_tcgen05_kernel<BN, STAGES, GATED>, smem, configured)) return rc;
     // persistent: one block per SM (its shared memory fills one), fewer if there are fewer tiles
     static int sm_counts[VX_MAX_DEVICES];
     const int sms = vx_sm_count(sm_counts);
-    const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+    const int tiles = (row_tiles ? max_row_tiles : (M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
     dim3 grid(tiles < sms ? tiles : sms);
     VX_LAUNCH_K(VX_K_GEMM, (gemm_tcgen05_kernel<BN, STAGES, GATED>), grid, TC_THREADS, smem, stream, ma, mw, bias, C, M,
-                N, K, ldc, act, error);
+                N, K, ldc, act, error, row_tiles, n_row_tiles);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -250,4 +259,23 @@ extern "C" int vx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
                      : tc_launch<256, 4, false>(ma, mw, bias, c, M, N, K, ldc, act, error, stream);
     return gated ? tc_launch<128, 6, true>(ma, mw, bias, c, M, N, K, ldc, act, error, stream)
                  : tc_launch<128, 6, false>(ma, mw, bias, c, M, N, K, ldc, act, error, stream);
+}
+
+// The grouped product of a routed feed-forward: A [rows, K] in group order, W [groups, N, K], row tiles of up to
+// 128 rows (group, first row, rows) whose number is on the device (at most max_row_tiles).  C [rows, N], or
+// [rows, N/2] = act(gate) * up when gated.
+extern "C" int vx_moe_gemm_tcgen05(const void* A, const void* W, void* C, int rows, int groups, int N, int K, int lda,
+                                   int ldc, int gated, int act, const int* row_tiles, const int* n_row_tiles,
+                                   int max_row_tiles, int* error, cudaStream_t stream) {
+    if (rows <= 0 || N <= 0 || max_row_tiles <= 0) return VX_OK;
+    if (K <= 0 || (K & 7) || (N & 15) || groups <= 0 || !error || !row_tiles || !n_row_tiles) return VX_ERR_SHAPE;
+    if ((lda & 7) || (ldc & 7) || lda < K) return VX_ERR_ALIGN;
+    if ((((uintptr_t)A) | ((uintptr_t)W) | ((uintptr_t)C)) & 15) return VX_ERR_ALIGN;
+    if (gated && (act < 0 || act > 3)) return VX_ERR_SHAPE;
+    if (ldc < (gated ? N / 2 : N) || (long long)groups * N > 0x7fffffffLL) return VX_ERR_SHAPE;
+    CUtensorMap ma, mw;
+    if (!tc_make_map(&ma, A, rows, K, lda, TC_BM) || !tc_make_map(&mw, W, groups * N, K, K, 256)) return VX_ERR_DRIVER;
+    bf16* c = (bf16*)C;
+    return gated ? tc_launch<256, 4, true>(ma, mw, nullptr, c, rows, N, K, ldc, act, error, stream, row_tiles, n_row_tiles, max_row_tiles)
+                 : tc_launch<256, 4, false>(ma, mw, nullptr, c, rows, N, K, ldc, act, error, stream, row_tiles, n_row_tiles, max_row_tiles);
 }

@@ -404,9 +404,31 @@ extern "C" int vx_moe_gemm(const void* A, int lda, const int* src_of_row, int sr
     return VX_OK;
 }
 
+// out[p, :] = x[src_of_row[p] / div, :] for the rows p of expert order (16 bytes a thread and step): the
+// activations in the order the tcgen05 grouped product reads them by TMA.
+__global__ void moe_gather_rows_kernel(const uint4* __restrict__ x, int ldx16, const int* __restrict__ src_of_row, int div,
+                                       uint4* __restrict__ out, int chunks) {
+    pdl_wait();
+    pdl_trigger();
+    const int p = blockIdx.x;
+    const uint4* src = x + (size_t)(src_of_row[p] / div) * ldx16;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) out[(size_t)p * chunks + c] = src[c];
+}
+
+extern "C" int vx_moe_gather_rows(const void* x, int ldx, const int* src_of_row, int div, void* out, int rows, int width,
+                                  cudaStream_t stream) {
+    if (rows <= 0) return VX_OK;
+    if (width <= 0 || width % 8 || ldx % 8 || div <= 0) return VX_ERR_SHAPE;
+    if ((((uintptr_t)x) | ((uintptr_t)out)) & 15) return VX_ERR_ALIGN;
+    VX_LAUNCH_K(VX_K_ELEMENTWISE, moe_gather_rows_kernel, rows, 128, 0, stream, (const uint4*)x, ldx / 8, src_of_row, div,
+                (uint4*)out, width / 8);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
 // out[t, :] = sum over k (ascending) of weight[t, k] * y[row_of[t * top + k], :] (+ shared[t, :]).
-template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of,
+template <typename T, typename TY>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ row_of,
                                    const float* __restrict__ weight, const T* __restrict__ shared_out,
                                    T* __restrict__ out, int width, int top) {
     pdl_wait();
@@ -415,23 +437,27 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top; ++k)
-            s = fmaf(weight[(size_t)t * top + k], y[(size_t)row_of[(size_t)t * top + k] * width + i], s);
+            s = fmaf(weight[(size_t)t * top + k], to_f32(y[(size_t)row_of[(size_t)t * top + k] * width + i]), s);
         if (shared_out) s += to_f32(shared_out[(size_t)t * width + i]);
         out[(size_t)t * width + i] = from_f32<T>(s);
     }
 }
 
-extern "C" int vx_moe_combine(const float* y, const int* row_of, const float* weight, const void* shared_out, void* out,
-                              int tokens, int width, int top, int dtype, cudaStream_t stream) {
+// y_dtype: the element type of the experts' rows (float32, or bfloat16 from the tcgen05 product).
+extern "C" int vx_moe_combine(const void* y, const int* row_of, const float* weight, const void* shared_out, void* out,
+                              int tokens, int width, int top, int dtype, int y_dtype, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
     if (width <= 0 || top <= 0) return VX_ERR_SHAPE;
     const int threads = width >= 1024 ? 256 : 128;
-    if (dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<float>), tokens, threads, 0, stream, y, row_of, weight,
-                    (const float*)shared_out, (float*)out, width, top);
-    else if (dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<bf16>), tokens, threads, 0, stream, y, row_of, weight,
-                    (const bf16*)shared_out, (bf16*)out, width, top);
+    if (dtype == VX_F32 && y_dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<float, float>), tokens, threads, 0, stream, (const float*)y, row_of,
+                    weight, (const float*)shared_out, (float*)out, width, top);
+    else if (dtype == VX_BF16 && y_dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<bf16, float>), tokens, threads, 0, stream, (const float*)y, row_of,
+                    weight, (const bf16*)shared_out, (bf16*)out, width, top);
+    else if (dtype == VX_BF16 && y_dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<bf16, bf16>), tokens, threads, 0, stream, (const bf16*)y, row_of,
+                    weight, (const bf16*)shared_out, (bf16*)out, width, top);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

@@ -81,7 +81,9 @@ def _declare(lib) -> None:
         "vx_linear_attention_chunked": [P, I, I, I, I, P, P, P, P, P, I, I, I, I, P],
         "vx_moe_route": [P, I, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, P],
         "vx_moe_gemm": [P, I, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, P],
-        "vx_moe_combine": [P, P, P, P, P, I, I, I, I, P],
+        "vx_moe_combine": [P, P, P, P, P, I, I, I, I, I, P],
+        "vx_moe_gather_rows": [P, I, P, I, P, I, I, P],
+        "vx_moe_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, P, P, I, P, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
         "vx_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "vx_gemm_tcgen05_pair": [P, P, P, P, I, I, I, I, I, I, I, I, P, P],
@@ -479,20 +481,24 @@ def linear_attention(x: torch.Tensor, q_col: int, k_col: int, v_col: int, decay:
                                       vdim, silu)
 
 
-MOE_TILE_ROWS = 64
+MOE_TILE_ROWS = 64            # row tiles of the mma.sync grouped product
+MOE_TCGEN05_TILE_ROWS = 128   # ... of the tcgen05 one
+MOE_TCGEN05_MIN_ROWS = 1024   # assignments of a step from which the tcgen05 grouped product is used
 
 
 class MoePlan:
     """What `moe_route` leaves on the device for the grouped products and the combination."""
-    __slots__ = ("chosen", "weight", "tiles", "n_tiles", "src_of_row", "row_of", "max_tiles", "top", "assignments")
+    __slots__ = ("chosen", "weight", "tiles", "n_tiles", "src_of_row", "row_of", "max_tiles", "top", "assignments",
+                 "tile_rows", "experts")
 
 
 _MOE_COUNTS = {}
 
 
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias, experts: int, top: int) -> MoePlan:
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias, experts: int, top: int,
+              tile_rows: int = MOE_TILE_ROWS) -> MoePlan:
     """Router logits in float32, the `top` largest per token, softmax over the chosen; then every
-    assignment's row in expert order and the row tiles of the grouped products."""
+    assignment's row in expert order and the row tiles (of up to `tile_rows` rows) of the grouped products."""
     _dev(h, w_router, bias)
     _need(h.stride(1) == 1 and w_router.dtype == torch.float32 and w_router.is_contiguous()
           and tuple(w_router.shape) == (experts, h.shape[1]), "moe_route: float32 router [experts, width]")
@@ -501,8 +507,8 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias, experts: int, top: 
     t, dev = h.shape[0], h.device
     a = t * top
     plan = MoePlan()
-    plan.top, plan.assignments = top, a
-    plan.max_tiles = -(-a // MOE_TILE_ROWS) + experts
+    plan.top, plan.assignments, plan.tile_rows, plan.experts = top, a, int(tile_rows), experts
+    plan.max_tiles = -(-a // plan.tile_rows) + experts
     ints = torch.empty(3 * a + (experts + 1) + 3 * plan.max_tiles + 1 + a, dtype=torch.int32, device=dev)
     plan.chosen, pos, plan.src_of_row, plan.row_of = ints[:a], ints[a:2 * a], ints[2 * a:3 * a], ints[3 * a:4 * a]
     rest = ints[4 * a:]
@@ -515,7 +521,7 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias, experts: int, top: 
         if not torch.cuda.is_current_stream_capturing():
             _MOE_COUNTS[key] = counts
     _check(library().vx_moe_route(_ptr(h), h.stride(0), _ptr(w_router), _ptr(bias), t, h.shape[1], experts, top,
-                                  MOE_TILE_ROWS, _ptr(plan.chosen), _ptr(plan.weight), _ptr(counts), _ptr(pos), _ptr(offsets),
+                                  plan.tile_rows, _ptr(plan.chosen), _ptr(plan.weight), _ptr(counts), _ptr(pos), _ptr(offsets),
                                   _ptr(plan.tiles), _ptr(plan.n_tiles), _ptr(plan.src_of_row), _ptr(plan.row_of),
                                   dtype_code(h.dtype), _stream()), "moe_route")
     return plan
@@ -531,6 +537,7 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gather: bool, out_
           "moe_gemm: a [rows, K], w [experts, N, K] of one element type")
     n, k = w.shape[1], w.shape[2]
     cols = n // 2 if gated_activation else n
+    _need(plan.tile_rows == MOE_TILE_ROWS, "moe_gemm: row tiles of %d" % MOE_TILE_ROWS)
     out = torch.empty((plan.assignments, cols), dtype=out_dtype, device=a.device)
     tc = (a.dtype == torch.bfloat16 and k % 8 == 0 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
           and w.data_ptr() % 16 == 0)
@@ -541,17 +548,53 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gather: bool, out_
     return out
 
 
+def moe_tcgen05_supported(h: torch.Tensor, assignments: int, n: int, k: int) -> bool:
+    """Whether a step's grouped products run on the tcgen05 tensor cores: bfloat16, enough rows, K a multiple of
+    8 and N of 16."""
+    return (h.dtype == torch.bfloat16 and assignments >= MOE_TCGEN05_MIN_ROWS and k % 8 == 0 and n % 16 == 0
+            and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0)
+
+
+def moe_gather_rows(x: torch.Tensor, plan: MoePlan) -> torch.Tensor:
+    """The tokens' rows of `x` in expert order, one per assignment."""
+    _dev(x)
+    _need(x.stride(1) == 1 and x.shape[1] % 8 == 0 and x.element_size() == 2, "moe_gather_rows: 16-bit rows of 8 n elements")
+    out = torch.empty((plan.assignments, x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(library().vx_moe_gather_rows(_ptr(x), x.stride(0), _ptr(plan.src_of_row), plan.top, _ptr(out), plan.assignments,
+                                        x.shape[1], _stream()), "moe_gather_rows")
+    return out
+
+
+def moe_gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gated_activation: Optional[str] = None) -> torch.Tensor:
+    """The grouped product on the tcgen05 tensor cores: `a` [assignments, K] bfloat16 IN EXPERT ORDER, w [experts, N, K];
+    the plan's row tiles must be of `MOE_TCGEN05_TILE_ROWS` rows.  bfloat16 out."""
+    _dev(a, w)
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and w.dim() == 3
+          and a.shape == (plan.assignments, w.shape[2]) and plan.tile_rows == MOE_TCGEN05_TILE_ROWS,
+          "moe_gemm_tcgen05: bfloat16 a [assignments, K] in expert order, w [experts, N, K], row tiles of 128")
+    n, k = w.shape[1], w.shape[2]
+    cols = n // 2 if gated_activation else n
+    out = torch.empty((plan.assignments, cols), dtype=torch.bfloat16, device=a.device)
+    _check(library().vx_moe_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(out), plan.assignments, w.shape[0], n, k, a.stride(0), cols,
+                                         1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0), _ptr(plan.tiles),
+                                         _ptr(plan.n_tiles), plan.max_tiles, _ptr(_error_word(a.device)), _stream()),
+           "moe_gemm_tcgen05")
+    note_bounded_wait()
+    return out
+
+
 def moe_combine(y: torch.Tensor, plan: MoePlan, shared_out, out_dtype: torch.dtype) -> torch.Tensor:
-    """Per token the weighted sum of its experts' rows of `y` (float32, expert order), plus `shared_out`."""
+    """Per token the weighted sum of its experts' rows of `y` (expert order; float32, or the result's element
+    type), plus `shared_out`."""
     _dev(y, shared_out)
-    _need(y.dtype == torch.float32 and y.is_contiguous(), "moe_combine: float32 rows")
+    _need(y.dtype in (torch.float32, out_dtype) and y.is_contiguous(), "moe_combine: float32 rows, or rows of the result's type")
     t = plan.assignments // plan.top
     if shared_out is not None:
         _need(shared_out.dtype == out_dtype and shared_out.is_contiguous() and tuple(shared_out.shape) == (t, y.shape[1]),
               "moe_combine: the shared expert's output in the result's shape and element type")
     out = torch.empty((t, y.shape[1]), dtype=out_dtype, device=y.device)
     _check(library().vx_moe_combine(_ptr(y), _ptr(plan.row_of), _ptr(plan.weight), _ptr(shared_out), _ptr(out), t, y.shape[1],
-                                    plan.top, dtype_code(out_dtype), _stream()), "moe_combine")
+                                    plan.top, dtype_code(out_dtype), dtype_code(y.dtype), _stream()), "moe_combine")
     return out
 
 

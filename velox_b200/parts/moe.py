@@ -77,6 +77,15 @@ class RoutedExperts(FeedForward):
             self.shared.bind(tensors, runtime)
 
     def forward(self, h: torch.Tensor, ctx=None) -> torch.Tensor:
+        i, e = self.intermediate_size, self.hidden_size
+        if self.tile and ops.moe_tcgen05_supported(h, h.shape[0] * self.top, 2 * i, e) and i % 8 == 0 and e % 16 == 0:
+            # a prompt portion: the tokens' rows are copied into expert order once, and both grouped products run on
+            # the tcgen05 tensor cores over row tiles of 128 (operands by TMA, the activation on the accumulators)
+            plan = ops.moe_route(h, self.router, self.bias, self.experts, self.top, ops.MOE_TCGEN05_TILE_ROWS)
+            a = ops.moe_gemm_tcgen05(ops.moe_gather_rows(h, plan), self.gate_up, plan, gated_activation=self.activation)
+            y = ops.moe_gemm_tcgen05(a, self.down, plan)
+            shared = self.shared.forward(h, ctx) if self.shared is not None else None
+            return ops.moe_combine(y, plan, shared, h.dtype)
         plan = ops.moe_route(h, self.router, self.bias, self.experts, self.top)
         if self.tile:
             a = ops.moe_gemm(h, self.gate_up, plan, True, h.dtype, gated_activation=self.activation)
