@@ -353,7 +353,7 @@ def dobepel_kernels(pk, sz, timed):
     state = torch.zeros((B, HL, D, D), device=dev)
     lin_fl = T * HL * 2.0 * (32 * 2 * D + 2 * D * D)   # scores and values within chunks of 64 (half of them), state read and update
     slot0, cu_b, slots_b = ints([0]), ints(list(range(B + 1))), ints(list(range(B)))
-    row("prompt linear attention, chunked (mma.sync, halves)", us(lambda: ops.linear_attention(
+    row("prompt linear attention, chunks side by side (mma.sync, halves)", us(lambda: ops.linear_attention(
         x, 0, HL * D, 2 * HL * D, decay, state, cu, slot0, 1, T, HL, D, D)), lin_fl)
     xd = (torch.randn((B, 4 * HL * D), device=dev) * 0.5).to(bf)
     row("decode linear attention, recurrent", us(lambda: ops.linear_attention(
@@ -371,6 +371,14 @@ def dobepel_kernels(pk, sz, timed):
     row("experts down, %d rows (grouped mma.sync)" % (T * top), us(lambda: ops.moe_gemm(a, dn, plan, False, torch.float32)),
         2.0 * T * top * F * E)
     row("router and plan, %d tokens" % T, us(lambda: ops.moe_route(h, wr, None, NE, top)), 0.0, T * E * 2.0)
+    plan128 = ops.moe_route(h, wr, None, NE, top, ops.MOE_TCGEN05_TILE_ROWS)
+    hs = ops.moe_gather_rows(h, plan128)
+    a128 = ops.moe_gemm_tcgen05(hs, gu, plan128, gated_activation="silu")
+    row("experts: rows into expert order, %d rows" % (T * top), us(lambda: ops.moe_gather_rows(h, plan128)), 0.0, 2.0 * T * top * E * 2)
+    row("experts gate_up, %d rows (grouped tcgen05, fused activation)" % (T * top),
+        us(lambda: ops.moe_gemm_tcgen05(hs, gu, plan128, gated_activation="silu")), 2.0 * T * top * 2 * F * E)
+    row("experts down, %d rows (grouped tcgen05)" % (T * top), us(lambda: ops.moe_gemm_tcgen05(a128, dn, plan128)),
+        2.0 * T * top * F * E)
     I = top * F + sz["shared_ff"]
     wq = (torch.randn((2 * I, E), device=dev) * 0.02).to(bf)
     row("Qwen3 gate_up, %d rows (tcgen05, fused activation)" % T, us(lambda: ops.gemm_tcgen05(

@@ -94,13 +94,13 @@ def test_gated_norm_and_activation(dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,Dk,Dv", [(3, 10, 40), (2, 64, 32), (1, 128, 128), (2, 7, 5), (3, 32, 96), (2, 32, 64), (2, 64, 192)])
 def test_decayed_linear_attention_carries_its_state(dtype, H, Dk, Dv):
-    """Three requests of 237, 1 and 270 tokens in portions (some of them single tokens) against the whole sequences;
+    """Three requests of 337, 1 and 570 tokens in portions (some of them single tokens) against the whole sequences;
     a far token's contribution survives hundreds of steps under a decay of 1 and dies under a small one.  In bfloat16
-    the steps with a portion of 32 tokens or more run in the chunked kernel (sizes it takes), the others in the
-    recurrent one: both must carry the same state."""
+    the steps with a portion of 32 tokens or more run in the chunked kernel (sizes it takes), those with one of 256 or
+    more with their chunks side by side, the others in the recurrent kernel: all must carry the same state."""
     from velox_b200.csrc import ops
     rng = np.random.default_rng(Dk)
-    lens = [237, 1, 270]
+    lens = [337, 1, 570]
     decay = np.asarray(([1.0, 0.9, 0.3] * H)[:H])
     W = 2 * H * Dk + H * Dv + 3   # (three columns of something else at the end of the packed rows)
     xs = [bf(rng.normal(size=(n, W))) for n in lens]
@@ -115,7 +115,7 @@ def test_decayed_linear_attention_carries_its_state(dtype, H, Dk, Dv):
     slots = [4, 1, 2]
     for s in slots:
         state[s].zero_()
-    cuts = [[20, 1, 1, 215], [1], [2, 133, 1, 134]]
+    cuts = [[20, 1, 1, 315], [1], [2, 433, 1, 134]]
     at, got = [0, 0, 0], [[], [], []]
     for step in range(4):
         rows, cu, sl, who = [], [0], [], []

@@ -79,6 +79,7 @@ def _declare(lib) -> None:
         "vx_kv_store": [P, I, I, I, P, P, P, I, I, I, I, I, I, P],
         "vx_linear_attention_recurrent": [P, I, I, I, I, P, P, P, P, P, I, I, I, I, I, I, P],
         "vx_linear_attention_chunked": [P, I, I, I, I, P, P, P, P, P, I, I, I, I, P],
+        "vx_linear_attention_parallel": [P, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P],
         "vx_moe_route": [P, I, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, P],
         "vx_moe_gemm": [P, I, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, P],
         "vx_moe_combine": [P, P, P, P, P, I, I, I, I, I, P],
@@ -450,6 +451,7 @@ LINEAR_ATTENTION_MAX_DIM = 256
 
 
 LINEAR_ATTENTION_CHUNKED_MIN_TOKENS = 32   # longest portion of a step from which the chunked kernel is used
+LINEAR_ATTENTION_PARALLEL_MIN_TOKENS = 256  # ... from which the chunks are worked on side by side
 
 
 def linear_attention_chunked_supported(dtype, dim: int, vdim: int) -> bool:
@@ -473,6 +475,15 @@ def linear_attention(x: torch.Tensor, q_col: int, k_col: int, v_col: int, decay:
         qkv = act(x[:, q_col:q_col + width], "silu") if silu else x[:, q_col:q_col + width]
         if qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
             out = torch.empty((x.shape[0], heads * vdim), dtype=torch.float32, device=x.device)
+            if max_new >= LINEAR_ATTENTION_PARALLEL_MIN_TOKENS:
+                # long portions: every chunk's own contribution, a scan over the chunks, every chunk's outputs
+                max_chunks = x.shape[0] // 64 + int(seqs)
+                scratch = workspace(x.device, max_chunks * heads * dim * vdim, which="linear_attention")
+                _check(library().vx_linear_attention_parallel(
+                    _ptr(qkv), qkv.stride(0), 0, heads * dim, 2 * heads * dim, _ptr(decay), _ptr(state), _ptr(scratch),
+                    _ptr(cu_seqlens), _ptr(state_slots), _ptr(out), int(seqs), max_chunks, heads, dim, vdim, _stream()),
+                    "linear_attention_parallel")
+                return out
             _check(library().vx_linear_attention_chunked(_ptr(qkv), qkv.stride(0), 0, heads * dim, 2 * heads * dim, _ptr(decay),
                                                          _ptr(state), _ptr(cu_seqlens), _ptr(state_slots), _ptr(out),
                                                          int(seqs), heads, dim, vdim, _stream()), "linear_attention_chunked")
