@@ -169,15 +169,35 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                 vis[kg] = key0 < warp_hi && (key0 + 16 > warp_lo || key0 < kept);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) sc[kg][0][c] = sc[kg][1][c] = 0.f;
-                if (!vis[kg]) continue;
-                const int r = kg * 16 + rr;
+            }
+            if (vis[0] && vis[1] && vis[2] && vis[3]) {
+                // the common tile, wholly visible to the warp: k steps outermost, so that the eight accumulators
+                // of a step are independent and their multiply-accumulates overlap
 #pragma unroll
                 for (int kk = 0; kk < DK / 16; ++kk) {
                     const int cc = 2 * kk + (mi & 1);
-                    unsigned b00, b01, b10, b11;
-                    ldmatrix_x4(b00, b01, b10, b11, ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4));
-                    mma_bf16(sc[kg][0], qf[kk], b00, b01);
-                    mma_bf16(sc[kg][1], qf[kk], b10, b11);
+#pragma unroll
+                    for (int kg = 0; kg < AB_BN / 16; ++kg) {
+                        const int r = kg * 16 + rr;
+                        unsigned b00, b01, b10, b11;
+                        ldmatrix_x4(b00, b01, b10, b11, ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4));
+                        mma_bf16(sc[kg][0], qf[kk], b00, b01);
+                        mma_bf16(sc[kg][1], qf[kk], b10, b11);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int kg = 0; kg < AB_BN / 16; ++kg) {
+                    if (!vis[kg]) continue;
+                    const int r = kg * 16 + rr;
+#pragma unroll
+                    for (int kk = 0; kk < DK / 16; ++kk) {
+                        const int cc = 2 * kk + (mi & 1);
+                        unsigned b00, b01, b10, b11;
+                        ldmatrix_x4(b00, b01, b10, b11, ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4));
+                        mma_bf16(sc[kg][0], qf[kk], b00, b01);
+                        mma_bf16(sc[kg][1], qf[kk], b10, b11);
+                    }
                 }
             }
 #pragma unroll
@@ -235,14 +255,22 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                 }
                 const int r = kg * 16 + ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
-                for (int nt = 0; nt < DV / 8; nt += 2) {
-                    const int cc = nt + (mi >> 1);
-                    unsigned v00, v01, v10, v11;
-                    ldmatrix_x4_trans(v00, v01, v10, v11, vs + r * (DV * 2) + (ab_swz<VCH>(r, cc) << 4));
-                    mma_bf16(o[nt], hi, v00, v01);
-                    mma_bf16(o[nt + 1], hi, v10, v11);
-                    mma_bf16(o[nt], lw, v00, v01);
-                    mma_bf16(o[nt + 1], lw, v10, v11);
+                for (int nt = 0; nt < DV / 8; nt += 4) {   // (two loads, then four independent pairs of products)
+                    unsigned v[2][4];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+                        ldmatrix_x4_trans(v[u][0], v[u][1], v[u][2], v[u][3],
+                                          vs + r * (DV * 2) + (ab_swz<VCH>(r, nt + 2 * u + (mi >> 1)) << 4));
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        mma_bf16(o[nt + 2 * u], hi, v[u][0], v[u][1]);
+                        mma_bf16(o[nt + 2 * u + 1], hi, v[u][2], v[u][3]);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        mma_bf16(o[nt + 2 * u], lw, v[u][0], v[u][1]);
+                        mma_bf16(o[nt + 2 * u + 1], lw, v[u][2], v[u][3]);
+                    }
                 }
             }
         }
