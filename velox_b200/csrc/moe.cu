@@ -30,6 +30,7 @@ __device__ __forceinline__ void route_load8(const bf16* p, float (&v)[8]) {
     for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
 }
 
+#define ROUTE_KC 512
 // `vec`: K a multiple of 8 and 16-byte aligned rows (the host checks); else element by element.
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -42,28 +43,47 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
-    if (t >= tokens) return;
-    const T* row = h + (size_t)t * ldh;
+    const bool valid = t < tokens;
+    const T* row = h + (size_t)(valid ? t : 0) * ldh;
     float* z = z_s[warp];
     if (vec) {
-        // eight experts at a time: a lane takes 8 consecutive k of the token's row (one 16-byte load for a bfloat16
-        // row) and the same 8 of each expert's row, so that 17 independent loads are in flight per step
+        // Eight experts at a time, 512 k at a time: the block brings that piece of the router's matrix into shared
+        // memory with every thread's loads in flight at once (read one after the other by a single warp they cost a
+        // memory latency each: 25 us for 8 experts of 2,048), then each warp takes its token's 8 dot products from there.
+        __shared__ __align__(16) float w_s[8][ROUTE_KC];
         for (int e0 = 0; e0 < E; e0 += 8) {
             float acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            for (int k = lane * 8; k < K; k += 256) {
-                float hv[8];
-                route_load8(row + k, hv);
+            for (int k0 = 0; k0 < K; k0 += ROUTE_KC) {
+                __syncthreads();
+                float4 v[8];   // (a block of 128 threads: 8 loads each, all asked for before any is stored)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (e0 + j < E) {
-                        const float4 a = *reinterpret_cast<const float4*>(w_router + (size_t)(e0 + j) * K + k);
-                        const float4 b = *reinterpret_cast<const float4*>(w_router + (size_t)(e0 + j) * K + k + 4);
-                        acc[j] = fmaf(hv[0], a.x, acc[j]); acc[j] = fmaf(hv[1], a.y, acc[j]);
-                        acc[j] = fmaf(hv[2], a.z, acc[j]); acc[j] = fmaf(hv[3], a.w, acc[j]);
-                        acc[j] = fmaf(hv[4], b.x, acc[j]); acc[j] = fmaf(hv[5], b.y, acc[j]);
-                        acc[j] = fmaf(hv[6], b.z, acc[j]); acc[j] = fmaf(hv[7], b.w, acc[j]);
+                for (int u = 0; u < 8; ++u) {
+                    const int idx = threadIdx.x + u * 128;
+                    const int e = idx / (ROUTE_KC / 4), c = (idx % (ROUTE_KC / 4)) * 4;
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (k0 + c < K) v[u] = *reinterpret_cast<const float4*>(w_router + (size_t)min(e0 + e, E - 1) * K + k0 + c);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int idx = threadIdx.x + u * 128;
+                    *reinterpret_cast<float4*>(&w_s[idx / (ROUTE_KC / 4)][(idx % (ROUTE_KC / 4)) * 4]) = v[u];
+                }
+                __syncthreads();
+                if (valid) {
+                    for (int kk = lane * 8; kk < ROUTE_KC && k0 + kk < K; kk += 256) {
+                        float hv[8];
+                        route_load8(row + k0 + kk, hv);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 a = *reinterpret_cast<const float4*>(&w_s[j][kk]);
+                            const float4 b = *reinterpret_cast<const float4*>(&w_s[j][kk + 4]);
+                            acc[j] = fmaf(hv[0], a.x, acc[j]); acc[j] = fmaf(hv[1], a.y, acc[j]);
+                            acc[j] = fmaf(hv[2], a.z, acc[j]); acc[j] = fmaf(hv[3], a.w, acc[j]);
+                            acc[j] = fmaf(hv[4], b.x, acc[j]); acc[j] = fmaf(hv[5], b.y, acc[j]);
+                            acc[j] = fmaf(hv[6], b.z, acc[j]); acc[j] = fmaf(hv[7], b.w, acc[j]);
+                        }
                     }
                 }
             }
@@ -73,7 +93,7 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
                 if (lane == 0 && e0 + j < E) z[e0 + j] = s + (bias ? bias[e0 + j] : 0.f);
             }
         }
-    } else {
+    } else if (valid) {
         for (int e = 0; e < E; ++e) {
             const float* w = w_router + (size_t)e * K;
             float s = 0.f;
@@ -82,6 +102,7 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
             if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
         }
     }
+    if (!valid) return;
     __syncwarp();
     for (int i = 0; i < top; ++i) {
         float best = -INFINITY;
@@ -309,13 +330,16 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
     };
 
     const int nk = (K + MT_BK - 1) / MT_BK;
-    load_stage(0, 0);
-    if (nk > 1) load_stage(1, MT_BK); else cp_async_commit();
+#pragma unroll
+    for (int st = 0; st < MT_STAGES - 1; ++st) {
+        if (st < nk) load_stage(st, st * MT_BK); else cp_async_commit();
+    }
     for (int kb = 0; kb < nk; ++kb) {
         const int cur = kb % MT_STAGES;
-        cp_async_wait<1>();   // all but the newest group have landed: stage `cur` is there
+        cp_async_wait<MT_STAGES - 2>();   // all but the newest groups have landed: stage `cur` is there
         __syncthreads();      // ... for every thread's copies, and everybody is done with the stage filled next
-        if (kb + 2 < nk) load_stage((kb + 2) % MT_STAGES, (kb + 2) * MT_BK); else cp_async_commit();
+        if (kb + MT_STAGES - 1 < nk) load_stage((kb + MT_STAGES - 1) % MT_STAGES, (kb + MT_STAGES - 1) * MT_BK);
+        else cp_async_commit();
 #pragma unroll
         for (int ks = 0; ks < MT_BK; ks += 16) {
             unsigned a[2][4], b[4][2];
@@ -431,13 +455,19 @@ template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ row_of,
                                    const float* __restrict__ weight, const T* __restrict__ shared_out,
                                    T* __restrict__ out, int width, int top) {
+    __shared__ int row_s[MOE_MAX_TOP];
+    __shared__ float w_s[MOE_MAX_TOP];
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
+    if (threadIdx.x < top) {
+        row_s[threadIdx.x] = row_of[(size_t)t * top + threadIdx.x];
+        w_s[threadIdx.x] = weight[(size_t)t * top + threadIdx.x];
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k)
-            s = fmaf(weight[(size_t)t * top + k], to_f32(y[(size_t)row_of[(size_t)t * top + k] * width + i]), s);
+        for (int k = 0; k < top; ++k) s = fmaf(w_s[k], to_f32(y[(size_t)row_s[k] * width + i]), s);
         if (shared_out) s += to_f32(shared_out[(size_t)t * width + i]);
         out[(size_t)t * width + i] = from_f32<T>(s);
     }
@@ -448,6 +478,7 @@ extern "C" int vx_moe_combine(const void* y, const int* row_of, const float* wei
                               int tokens, int width, int top, int dtype, int y_dtype, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
     if (width <= 0 || top <= 0) return VX_ERR_SHAPE;
+    if (top > MOE_MAX_TOP) return VX_ERR_LIMIT;
     const int threads = width >= 1024 ? 256 : 128;
     if (dtype == VX_F32 && y_dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<float, float>), tokens, threads, 0, stream, (const float*)y, row_of,
