@@ -384,7 +384,7 @@ def dobepel_kernels(pk, sz, timed):
     row("Qwen3 gate_up, %d rows (tcgen05, fused activation)" % T, us(lambda: ops.gemm_tcgen05(
         h, wq, None, gated_activation="silu", pair=ops.tcgen05_pair_better(T, 2 * I, h.device))), 2.0 * T * 2 * I * E)
     hd = torch.randn((B, E), device=dev).to(bf)
-    pland = ops.moe_route(hd, wr, None, NE, top)
+    pland = ops.moe_route(hd, wr, None, NE, top, ops.moe_tile_rows(hd, B * top))
     many = [(torch.randn((NE, 2 * F, E), device=dev) * 0.02).to(bf) for _ in range(max(2, int(3e8 // (NE * 2 * F * E * 2))))]
     k = [0]
 
@@ -392,7 +392,8 @@ def dobepel_kernels(pk, sz, timed):
         k[0] = (k[0] + 1) % len(many)
         ops.moe_gemm(hd, many[k[0]], pland, True, bf, gated_activation="silu")
     touched = min(NE, B * top)
-    row("experts gate_up, %d tokens (decode)" % B, us(experts_decode, 50), 0.0, touched * 2 * F * E * 2.0)
+    row("experts gate_up, %d tokens (decode, grouped mma.sync, row tiles of 16)" % B, us(experts_decode, 50), 0.0,
+        touched * 2 * F * E * 2.0)
     manyq = [(torch.randn((2 * I, E), device=dev) * 0.02).to(bf) for _ in range(max(2, int(3e8 // (2 * I * E * 2))))]
 
     def dense_decode():

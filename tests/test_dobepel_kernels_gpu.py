@@ -224,11 +224,13 @@ def test_one_key_that_stands_out_is_seen_exactly_where_the_mask_says(kernel, dty
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("E,top,K,F,shared", [(3, 1, 40, 12, False), (8, 3, 64, 48, True), (5, 5, 72, 16, True), (16, 2, 128, 64, False)])
-def test_router_grouped_products_and_combination(dtype, E, top, K, F, shared):
+@pytest.mark.parametrize("E,top,K,F,shared,T", [(3, 1, 40, 12, False, 150), (8, 3, 64, 48, True, 150), (5, 5, 72, 16, True, 150),
+                                                 (16, 2, 128, 64, False, 150), (8, 3, 64, 48, True, 9), (16, 2, 128, 64, False, 40),
+                                                 (4, 1, 200, 24, True, 1)])
+def test_router_grouped_products_and_combination(dtype, E, top, K, F, shared, T):
+    """150 tokens: row tiles of 64; 1, 9 and 40 tokens: in bfloat16 the row tiles of 16 of a decode step."""
     from velox_b200.csrc import ops
     rng = np.random.default_rng(E * top)
-    T = 150
     h = bf(rng.normal(size=(T, K)))
     wr, b = bf(rng.normal(size=(E, K)) * 0.5), bf(rng.normal(size=E))
     w = {"router": wr, "router.b": b}
@@ -238,7 +240,9 @@ def test_router_grouped_products_and_combination(dtype, E, top, K, F, shared):
     cfg = {"router": {"experts": E, "top": top}, "shared": None}
     want = D.routed_ff(h, w, "", cfg)
     chosen, weight = D.route(h, wr, b, top)
-    plan = ops.moe_route(dev(h, dtype), dev(wr), dev(b), E, top)
+    rows_per_tile = ops.moe_tile_rows(dev(h, dtype), T * top) if F % 8 == 0 else ops.MOE_TILE_ROWS
+    assert rows_per_tile == (16 if dtype == torch.bfloat16 and T * top <= 256 and F % 8 == 0 and K % 8 == 0 else 64)
+    plan = ops.moe_route(dev(h, dtype), dev(wr), dev(b), E, top, rows_per_tile)
     assert (plan.chosen.view(T, top).cpu().numpy() == chosen).all()
     close(plan.weight, weight, 1e-5)
     # every assignment has a row of its own in expert order, experts ascending
@@ -258,7 +262,7 @@ def test_router_grouped_products_and_combination(dtype, E, top, K, F, shared):
     got = ops.moe_combine(y, plan, dev(extra, dtype) if shared else None, dtype)
     close(got, want + (extra if shared else 0.0), TOL[dtype])
     # a second call on the same stream starts from clean counters
-    plan2 = ops.moe_route(dev(h, dtype), dev(wr), dev(b), E, top)
+    plan2 = ops.moe_route(dev(h, dtype), dev(wr), dev(b), E, top, rows_per_tile)
     assert sorted(plan2.row_of.cpu().numpy().tolist()) == list(range(T * top))
 
 

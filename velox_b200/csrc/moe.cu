@@ -390,16 +390,126 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
     }
 }
 
+// The same for steps of few tokens (decode): row tiles of 16, so that a step's handful of rows per expert costs
+// one m16 tile of products, not four; a block of 4 warps owns 16 rows x 64 columns (16 columns a warp) and
+// streams its 64 rows of W through four stages.
+#define MS_BM 16
+#define MS_STAGES 4
+#define MS_SMEM (MS_STAGES * (MS_BM + MT_BN) * MT_LD * 2)
+
+template <typename TC>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma16_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ src_of_row, int src_div,
+                      const bf16* __restrict__ W, const int* __restrict__ tiles, const int* __restrict__ n_tiles,
+                      TC* __restrict__ C, int ldc, int N, int K, int gated, int act) {
+    extern __shared__ __align__(16) unsigned char ms_smem[];
+    typedef bf16 (*TileA)[MS_BM][MT_LD];
+    typedef bf16 (*TileW)[MT_BN][MT_LD];
+    TileA As = reinterpret_cast<TileA>(ms_smem);
+    TileW Ws = reinterpret_cast<TileW>(ms_smem + MS_STAGES * MS_BM * MT_LD * 2);
+    __shared__ int src_s[MS_BM];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * MT_BN;
+    pdl_wait();
+    pdl_trigger();
+    if ((int)blockIdx.y >= n_tiles[0]) return;
+    const int e = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    const bf16* We = W + (size_t)e * N * K;
+    if (tid < MS_BM) {
+        const int p = row0 + tid;
+        src_s[tid] = tid < rows ? (src_of_row ? src_of_row[p] / src_div : p) : -1;
+    }
+    __syncthreads();
+    const int wn = warp * 16;
+    float acc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+    auto load_stage = [&](int stage, int k0) {
+        {   // 16 rows x 8 chunks of A: one a thread
+            const int r = tid >> 3, ck = (tid & 7) * 8;
+            bf16* da = &As[stage][r][ck];
+            const int s = src_s[r];
+            if (s >= 0 && k0 + ck < K) cp_async16(da, A + (size_t)s * lda + k0 + ck);
+            else *reinterpret_cast<uint4*>(da) = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {   // 64 rows x 8 chunks of W: four a thread
+            const int idx = tid + it * 128;
+            const int r = idx >> 3, ck = (idx & 7) * 8;
+            bf16* dw = &Ws[stage][r][ck];
+            if (n0 + r < N && k0 + ck < K) cp_async16(dw, We + (size_t)(n0 + r) * K + k0 + ck);
+            else *reinterpret_cast<uint4*>(dw) = make_uint4(0, 0, 0, 0);
+        }
+        cp_async_commit();
+    };
+    const int nk = (K + MT_BK - 1) / MT_BK;
+#pragma unroll
+    for (int st = 0; st < MS_STAGES - 1; ++st) {
+        if (st < nk) load_stage(st, st * MT_BK); else cp_async_commit();
+    }
+    for (int kb = 0; kb < nk; ++kb) {
+        const int cur = kb % MS_STAGES;
+        cp_async_wait<MS_STAGES - 2>();
+        __syncthreads();
+        if (kb + MS_STAGES - 1 < nk) load_stage((kb + MS_STAGES - 1) % MS_STAGES, (kb + MS_STAGES - 1) * MT_BK);
+        else cp_async_commit();
+#pragma unroll
+        for (int ks = 0; ks < MT_BK; ks += 16) {
+            unsigned a[4], r0, r1, r2, r3;
+            ldmatrix_x4(a[0], a[1], a[2], a[3], &As[cur][lane & 15][ks + (lane >> 4) * 8]);
+            ldmatrix_x4(r0, r1, r2, r3, &Ws[cur][wn + (lane & 7) + ((lane >> 4) << 3)][ks + ((lane >> 3) & 1) * 8]);
+            mma_bf16(acc[0], a, r0, r1);
+            mma_bf16(acc[1], a, r2, r3);
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = (lane >> 2) + 8 * half;
+        if (r >= rows) continue;
+        TC* crow = C + (size_t)(row0 + r) * ldc;
+        const int n = n0 + wn + 2 * (lane & 3);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            if (gated) {   // the warp's 16 columns: 8 gates, then their 8 ups
+                if (n + c < N)
+                    crow[((n + c) >> 4) * 8 + ((n + c) & 7)] =
+                        from_f32<TC>(activation(acc[0][2 * half + c], act) * acc[1][2 * half + c]);
+            } else {
+                if (n + c < N) crow[n + c] = from_f32<TC>(acc[0][2 * half + c]);
+                if (n + 8 + c < N) crow[n + 8 + c] = from_f32<TC>(acc[1][2 * half + c]);
+            }
+        }
+    }
+}
+
 // in_dtype: A and W; out_dtype: C.  `tensor_cores`: the bfloat16 kernel (K a multiple of 8,
 // 16-byte aligned rows); else the multiply-add kernel.  max_tiles bounds the tiles of any step.
+// tile_rows: 64, or 16 (tensor cores only) for steps of few tokens.
 extern "C" int vx_moe_gemm(const void* A, int lda, const int* src_of_row, int src_div, const void* W, const int* tiles,
                            const int* n_tiles, int max_tiles, void* C, int ldc, int N, int K, int gated, int act,
-                           int in_dtype, int out_dtype, int tensor_cores, cudaStream_t stream) {
+                           int in_dtype, int out_dtype, int tensor_cores, int tile_rows, cudaStream_t stream) {
     if (max_tiles <= 0 || N <= 0) return VX_OK;
     if (K <= 0 || lda < K || src_div <= 0 || (gated && N % 16)) return VX_ERR_SHAPE;
     if (max_tiles > 65535) return VX_ERR_LIMIT;
+    if (tile_rows != MT_BM && !(tile_rows == MS_BM && tensor_cores)) return VX_ERR_SHAPE;
     dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
-    if (tensor_cores) {
+    if (tensor_cores && tile_rows == MS_BM) {
+        if (in_dtype != VX_BF16) return VX_ERR_DTYPE;
+        if (K % 8 || lda % 8 || (((uintptr_t)A) | ((uintptr_t)W)) & 15) return VX_ERR_ALIGN;
+        static bool conf_b[VX_MAX_DEVICES], conf_f[VX_MAX_DEVICES];
+        if (int rc = out_dtype == VX_BF16 ? vx_configure_smem(moe_gemm_mma16_kernel<bf16>, MS_SMEM, conf_b)
+                                          : vx_configure_smem(moe_gemm_mma16_kernel<float>, MS_SMEM, conf_f)) return rc;
+        if (out_dtype == VX_BF16)
+            VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_mma16_kernel<bf16>), grid, 128, MS_SMEM, stream, (const bf16*)A, lda, src_of_row,
+                        src_div, (const bf16*)W, tiles, n_tiles, (bf16*)C, ldc, N, K, gated, act);
+        else if (out_dtype == VX_F32)
+            VX_LAUNCH_K(VX_K_GEMM, (moe_gemm_mma16_kernel<float>), grid, 128, MS_SMEM, stream, (const bf16*)A, lda, src_of_row,
+                        src_div, (const bf16*)W, tiles, n_tiles, (float*)C, ldc, N, K, gated, act);
+        else
+            return VX_ERR_DTYPE;
+    } else if (tensor_cores) {
         if (in_dtype != VX_BF16) return VX_ERR_DTYPE;
         if (K % 8 || lda % 8 || (((uintptr_t)A) | ((uintptr_t)W)) & 15) return VX_ERR_ALIGN;
         static bool configured_b[VX_MAX_DEVICES], configured_f[VX_MAX_DEVICES];

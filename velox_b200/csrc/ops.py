@@ -81,7 +81,7 @@ def _declare(lib) -> None:
         "vx_linear_attention_chunked": [P, I, I, I, I, P, P, P, P, P, I, I, I, I, P],
         "vx_linear_attention_parallel": [P, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P],
         "vx_moe_route": [P, I, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, P],
-        "vx_moe_gemm": [P, I, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, P],
+        "vx_moe_gemm": [P, I, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, I, P],
         "vx_moe_combine": [P, P, P, P, P, I, I, I, I, I, P],
         "vx_moe_gather_rows": [P, I, P, I, P, I, I, P],
         "vx_moe_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, P, P, I, P, P],
@@ -493,6 +493,8 @@ def linear_attention(x: torch.Tensor, q_col: int, k_col: int, v_col: int, decay:
 
 
 MOE_TILE_ROWS = 64            # row tiles of the mma.sync grouped product
+MOE_SMALL_TILE_ROWS = 16      # ... for steps of few tokens (decode)
+MOE_SMALL_MAX_ROWS = 256      # assignments of a step up to which the small tiles are used
 MOE_TCGEN05_TILE_ROWS = 128   # ... of the tcgen05 one
 MOE_TCGEN05_MIN_ROWS = 1024   # assignments of a step from which the tcgen05 grouped product is used
 
@@ -548,15 +550,25 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gather: bool, out_
           "moe_gemm: a [rows, K], w [experts, N, K] of one element type")
     n, k = w.shape[1], w.shape[2]
     cols = n // 2 if gated_activation else n
-    _need(plan.tile_rows == MOE_TILE_ROWS, "moe_gemm: row tiles of %d" % MOE_TILE_ROWS)
     out = torch.empty((plan.assignments, cols), dtype=out_dtype, device=a.device)
-    tc = (a.dtype == torch.bfloat16 and k % 8 == 0 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
-          and w.data_ptr() % 16 == 0)
+    tc = moe_mma_supported(a, k) and w.data_ptr() % 16 == 0
+    _need(plan.tile_rows == MOE_TILE_ROWS or (plan.tile_rows == MOE_SMALL_TILE_ROWS and tc),
+          "moe_gemm: row tiles of %d, or of %d on the tensor cores" % (MOE_TILE_ROWS, MOE_SMALL_TILE_ROWS))
     _check(library().vx_moe_gemm(_ptr(a), a.stride(0), _ptr(plan.src_of_row) if gather else None, plan.top if gather else 1,
                                  _ptr(w), _ptr(plan.tiles), _ptr(plan.n_tiles), plan.max_tiles, _ptr(out), cols, n, k,
                                  1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0), dtype_code(a.dtype),
-                                 dtype_code(out_dtype), 1 if tc else 0, _stream()), "moe_gemm")
+                                 dtype_code(out_dtype), 1 if tc else 0, plan.tile_rows, _stream()), "moe_gemm")
     return out
+
+
+def moe_mma_supported(a: torch.Tensor, k: int) -> bool:
+    return a.dtype == torch.bfloat16 and k % 8 == 0 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+
+
+def moe_tile_rows(h: torch.Tensor, assignments: int) -> int:
+    """Row tiles for the `mma.sync` grouped products of a step: 16 rows for a handful of tokens, else 64."""
+    small = assignments <= MOE_SMALL_MAX_ROWS and moe_mma_supported(h, h.shape[1])
+    return MOE_SMALL_TILE_ROWS if small else MOE_TILE_ROWS
 
 
 def moe_tcgen05_supported(h: torch.Tensor, assignments: int, n: int, k: int) -> bool:

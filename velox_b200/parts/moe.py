@@ -86,7 +86,9 @@ class RoutedExperts(FeedForward):
             y = ops.moe_gemm_tcgen05(a, self.down, plan)
             shared = self.shared.forward(h, ctx) if self.shared is not None else None
             return ops.moe_combine(y, plan, shared, h.dtype)
-        plan = ops.moe_route(h, self.router, self.bias, self.experts, self.top)
+        # (a decode step's few rows per expert: row tiles of 16; the second product reads rows of `inner` elements)
+        rows = ops.moe_tile_rows(h, h.shape[0] * self.top) if i % 8 == 0 else ops.MOE_TILE_ROWS
+        plan = ops.moe_route(h, self.router, self.bias, self.experts, self.top, rows)
         if self.tile:
             a = ops.moe_gemm(h, self.gate_up, plan, True, h.dtype, gated_activation=self.activation)
         else:
