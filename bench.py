@@ -344,7 +344,7 @@ def dobepel_kernels(pk, sz, timed):
     seqs, pos = ints(list(range(B))), ints([CTX - 1] * B)
     nb = B * G * (win + keep) * 2 * D * 2.0
     row("decode attention, biased window", us(lambda: ops.biased_decode_attention(
-        qd, qd.shape[1], kp, vp, bt, seqs, pos, D ** -0.5, win, keep, 8.0, H, G, D, D, B), 50), 0.0, nb)
+        qd, qd.shape[1], kp, vp, bt, seqs, pos, D ** -0.5, win, keep, 8.0, H, G, D, D, B, max_kv=CTX), 50), 0.0, nb)
     row("decode attention, Qwen3", us(lambda: ops.paged_decode_attention(
         qd, qd.shape[1], kp, vp, bt, seqs, pos, D ** -0.5, win, H, G, D, B, CTX), 50), 0.0, B * G * win * 2 * D * 2.0)
     # -- linear attention --

@@ -164,8 +164,9 @@ def attend(kernel, q, kp, vp, table, rows, dtype, scale, size, keep_first, expon
     if kernel == "general":
         return ops.paged_attention_generic(*args, ints([0] * T), ints(rows), scale, size, H, G, Dk, T, v_head_dim=Dv,
                                            keep_first=keep_first, bias_exponent=exponent)
-    if kernel == "single":
-        return ops.biased_decode_attention(*args, ints([0] * T), ints(rows), scale, size, keep_first, exponent, H, G, Dk, Dv, T)
+    if kernel == "single":   # (few keys: one block a token and kv head; many: the keys cut into runs and joined)
+        return ops.biased_decode_attention(*args, ints([0] * T), ints(rows), scale, size, keep_first, exponent, H, G, Dk, Dv, T,
+                                           max_kv=max(rows) + 1)
     assert rows == list(range(rows[0], rows[0] + T))
     return ops.biased_prefill_attention(*args, ints([0, T]), ints([rows[0]]), scale, size, keep_first, exponent, H, G, Dk, Dv,
                                         1, T, T)
@@ -296,3 +297,22 @@ def test_grouped_products_on_the_tcgen05_tensor_cores(E, top, K, F, T):
     # as far from the exact result as the plain implementation with the same roundings, give or take
     g = got.float().cpu().numpy().astype(np.float64)
     assert np.sqrt(np.mean((g - exact) ** 2)) <= 1.3 * np.sqrt(np.mean((want - exact) ** 2)) + 1e-6
+
+
+@pytest.mark.parametrize("H,G,Dk,Dv,size,keep", [(8, 2, 128, 128, 1200, 4), (4, 4, 64, 32, 600, 0), (6, 2, 64, 64, 0, 0)])
+def test_single_tokens_with_many_keys_are_cut_into_runs(H, G, Dk, Dv, size, keep):
+    """Tokens deep in a sequence of 1,300 (a window of 600 or 1,200 keys, or every key) beside tokens near its start, in
+    one call: the long ones' keys are cut into runs for several blocks and joined, the short ones' runs are mostly empty."""
+    rng = np.random.default_rng(size + H)
+    T, S, scale = 1300, 16, 0.1
+    q, k, v = bf(rng.normal(size=(T, H, Dk))), bf(rng.normal(size=(T, G, Dk))), bf(rng.normal(size=(T, G, Dv)))
+    want = D.biased_window_attention(q, k, v, scale, size if size else T + 1, keep).reshape(T, H * Dv)
+    kp, vp, table = paged(k, v, S, 90, 7)
+    rows = [1299, 0, 700, 15, 16, 1200, 599, 600, 601, 3]
+    from velox_b200.csrc import ops
+    bt = torch.full((1, 128), -1, dtype=torch.int32, device=DEV)
+    bt[0, :len(table)] = ints(table)
+    qd = dev(q[rows].reshape(len(rows), H * Dk), torch.bfloat16)
+    got = ops.biased_decode_attention(qd, qd.shape[1], dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), bt, ints([0] * len(rows)),
+                                      ints(rows), scale, size, keep, 8.0, H, G, Dk, Dv, len(rows), max_kv=T)
+    close(got, want[rows], TOL[torch.bfloat16])

@@ -309,7 +309,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
                      const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
                      const int* __restrict__ seq_of_token, const int* __restrict__ positions, bf16* __restrict__ out,
                      int out_row_stride, float scale_log2, float bias_exp, int window, int keep_first, int H, int Hk,
-                     int S, int share_log2) {
+                     int S, int share_log2, float* __restrict__ scratch) {
     extern __shared__ __align__(128) unsigned char ad_smem[];
     constexpr int KCH = DK / 8, VCH = DV / 8;
     constexpr int K_BYTES = 16 * DK * 2, V_BYTES = 16 * DV * 2;
@@ -330,7 +330,12 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
     const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int nkept = window > 0 ? min(keep_first, start) : 0;
     const int nkeys = nkept + kv_len - start;
-    const int ngroups = (nkeys + 15) >> 4;
+    // with gridDim.z > 1 the groups of 16 keys are cut into as many runs, one a block; the runs' parts go to the
+    // scratch and a second kernel adds them in order
+    const int all_groups = (nkeys + 15) >> 4;
+    const int per_run = (all_groups + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int g_lo = (int)blockIdx.z * per_run;
+    const int ngroups = min(all_groups, g_lo + per_run);   // (one past this block's last group)
 
     for (int c = threadIdx.x; c < 16 * KCH; c += AD_WARPS * 32) {
         const int r = c / KCH, cc = c % KCH;
@@ -358,7 +363,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
                        v_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DV + cc * 8);
         }
     };
-    if (warp < ngroups) issue(warp, 0);
+    if (g_lo + warp < ngroups) issue(g_lo + warp, 0);
     cp_async_commit();
     __syncthreads();   // the queries are in shared memory
     const int mi = lane >> 3;
@@ -378,7 +383,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
     const float sl[2] = {bias_exp > 0.f ? exp2f(-bias_exp * (float)(hd0 + 1) / (float)H) * AB_LOG2E : 0.f,
                          bias_exp > 0.f ? exp2f(-bias_exp * (float)(hd1 + 1) / (float)H) * AB_LOG2E : 0.f};
     int it = 0;
-    for (int g = warp; g < ngroups; g += AD_WARPS, ++it) {
+    for (int g = g_lo + warp; g < ngroups; g += AD_WARPS, ++it) {
         const int stage = it & 1;
         if (g + AD_WARPS < ngroups) issue(g + AD_WARPS, stage ^ 1);
         cp_async_commit();
@@ -483,7 +488,34 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
             L += p[DV + 1] * f;
             acc += p[d] * f;
         }
-        out[(size_t)t * out_row_stride + (size_t)(head0 + r) * DV + d] = __float2bfloat16_rn(acc / L);
+        if (gridDim.z == 1) {
+            out[(size_t)t * out_row_stride + (size_t)(head0 + r) * DV + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            float* dst = scratch + (((size_t)t * H + head0 + r) * gridDim.z + blockIdx.z) * (DV + 2);
+            dst[d] = acc;
+            if (d == 0) { dst[DV] = M; dst[DV + 1] = L; }
+        }
+    }
+}
+
+// The runs' parts of one (token, head), added in order: out = sum_z acc_z 2^(M_z - M) / sum_z L_z 2^(M_z - M).
+__global__ void biased_decode_join_kernel(const float* __restrict__ scratch, bf16* __restrict__ out, int out_row_stride,
+                                          int H, int DV, int runs) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float* p = scratch + ((size_t)t * H + h) * runs * (DV + 2);
+    float M = -INFINITY;
+    for (int z = 0; z < runs; ++z) M = fmaxf(M, p[(size_t)z * (DV + 2) + DV]);
+    for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+        float L = 0.f, acc = 0.f;
+        for (int z = 0; z < runs; ++z) {
+            const float* q = p + (size_t)z * (DV + 2);
+            const float f = q[DV] == -INFINITY ? 0.f : exp2f(q[DV] - M);
+            L += q[DV + 1] * f;
+            acc += q[d] * f;
+        }
+        out[(size_t)t * out_row_stride + (size_t)h * DV + d] = __float2bfloat16_rn(acc / L);
     }
 }
 
@@ -491,7 +523,7 @@ template <int DK, int DV>
 static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool,
                                 const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
                                 bf16* out, int out_row_stride, float scale, float bias_exp, int window, int keep_first,
-                                int tokens, int H, int Hk, int S, cudaStream_t stream) {
+                                int tokens, int H, int Hk, int S, float* scratch, int runs, cudaStream_t stream) {
     const size_t walk = (size_t)AD_WARPS * 2 * (16 * DK * 2 + 16 * DV * 2), parts = (size_t)AD_WARPS * 16 * (DV + 2) * 4;
     const size_t smem = 16 * DK * 2 + (walk > parts ? walk : parts);
     static bool configured[VX_MAX_DEVICES];
@@ -500,10 +532,14 @@ static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_p
     int share_log2 = 0;
     if (G > 1 && G <= 16 && (G & (G - 1)) == 0)
         while ((1 << share_log2) < G) ++share_log2;
-    dim3 grid(share_log2 ? Hk : H, tokens);
+    if (runs < 1 || !scratch) runs = 1;
+    dim3 grid(share_log2 ? Hk : H, tokens, runs);
     VX_LAUNCH_K(VX_K_ATTENTION, (biased_decode_kernel<DK, DV>), grid, AD_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
                 v_pool, block_table, max_blocks, seq_of_token, positions, out, out_row_stride, scale * AB_LOG2E, bias_exp,
-                window, keep_first, H, Hk, S, share_log2);
+                window, keep_first, H, Hk, S, share_log2, scratch);
+    if (runs > 1)
+        VX_LAUNCH_K(VX_K_JOIN, biased_decode_join_kernel, dim3(tokens, H), DV >= 128 ? 128 : 64, 0, stream, (const float*)scratch,
+                    out, out_row_stride, H, DV, runs);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -529,12 +565,13 @@ static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, co
 }
 
 // Portions: cu_seqlens and kv_offsets given, `segments` requests of up to `max_new` tokens.  Single tokens:
-// cu_seqlens null, seq_of_token and positions given, `segments` token rows (max_new = 1).
+// cu_seqlens null, seq_of_token and positions given, `segments` token rows (max_new = 1); with `runs` > 1 and a
+// float32 scratch of segments * H * runs * (DV + 2) elements a token's keys are cut into runs, a block each.
 extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
                                    const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
                                    const int* seq_of_token, const int* positions, void* out, int out_row_stride,
                                    float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
-                                   int H, int Hk, int DK, int DV, int S, cudaStream_t stream) {
+                                   int H, int Hk, int DK, int DV, int S, float* scratch, int runs, cudaStream_t stream) {
     if (segments <= 0 || max_new <= 0) return VX_OK;
     if (H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
     if (cu_seqlens ? !kv_offsets : (!seq_of_token || !positions || max_new != 1)) return VX_ERR_SHAPE;
@@ -546,7 +583,7 @@ extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* 
     if (DK == K_ && DV == V_)                                                                                               \
         return launch_biased_decode<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,       \
                                             block_table, max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, \
-                                            scale, bias_exp, window, keep_first, segments, H, Hk, S, stream)
+                                            scale, bias_exp, window, keep_first, segments, H, Hk, S, scratch, runs, stream)
         AD_GO(64, 32); AD_GO(64, 64); AD_GO(64, 128); AD_GO(128, 32); AD_GO(128, 64); AD_GO(128, 128);
 #undef AD_GO
         return VX_ERR_SHAPE;

@@ -71,7 +71,7 @@ def _declare(lib) -> None:
         "vx_add_bias": [P, P, P, I, I, I, P],
         "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, I, I, F, P],
-        "vx_biased_attention": [P, I, P, P, P, I, P, P, P, P, P, I, F, F, I, I, I, I, I, I, I, I, I, P],
+        "vx_biased_attention": [P, I, P, P, P, I, P, P, P, P, P, I, F, F, I, I, I, I, I, I, I, I, I, P, I, P],
         "vx_embedding_pair": [P, P, P, P, P, P, P, P, P, I, I, I, I, c_longlong, c_longlong, I, P],
         "vx_merge_norm_add_norm": [P, P, P, F, P, P, F, P, F, P, P, I, I, F, I, P],
         "vx_act": [P, I, P, I, I, I, I, I, P],
@@ -294,6 +294,9 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
     return out
 
 
+BIASED_DECODE_MAX_RUNS = 8
+
+
 def biased_attention_supported(dtype, head_dim: int, v_head_dim: int, page_size: int) -> bool:
     """What the tensor-core kernel for attention with a bias by distance, a window with kept first positions
     and values of another size than keys takes."""
@@ -302,7 +305,7 @@ def biased_attention_supported(dtype, head_dim: int, v_head_dim: int, page_size:
 
 def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions,
                       scale, window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, segments,
-                      max_new, tokens, out):
+                      max_new, tokens, out, max_kv=0):
     _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions, out)
     _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
           "biased_attention: bfloat16 only")
@@ -312,11 +315,18 @@ def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, 
           "biased_attention: pools [pages, kv heads, page size, head size]")
     if out is None:
         out = torch.empty((tokens, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
+    # single tokens with many visible keys: the keys cut into runs of at least 16 groups of 16, 8 runs at most
+    runs, scratch = 1, None
+    if cu_seqlens is None and max_kv > 0:
+        keys = max_kv if window <= 0 else min(max_kv, window + keep_first)
+        runs = max(1, min(BIASED_DECODE_MAX_RUNS, -(-keys // 16) // 16))
+        if runs > 1:
+            scratch = workspace(q.device, tokens * num_heads * runs * (v_head_dim + 2), which="biased_decode")
     _check(library().vx_biased_attention(
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(cu_seqlens),
         _ptr(kv_offsets), _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * v_head_dim, float(scale),
         float(bias_exponent), int(window), int(keep_first), int(segments), int(max_new), num_heads, num_kv_heads, head_dim,
-        v_head_dim, k_pool.shape[2], _stream()), "biased_attention")
+        v_head_dim, k_pool.shape[2], _ptr(scratch), runs, _stream()), "biased_attention")
     return out
 
 
@@ -333,11 +343,13 @@ def biased_prefill_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_se
 
 def biased_decode_attention(q, q_row_stride, k_pool, v_pool, block_table, seq_of_token, positions, scale: float,
                             window: int, keep_first: int, bias_exponent: float, num_heads: int, num_kv_heads: int,
-                            head_dim: int, v_head_dim: int, tokens: int, out=None):
-    """The same for token rows that each stand alone: row t is request seq_of_token[t] at position positions[t]."""
+                            head_dim: int, v_head_dim: int, tokens: int, out=None, max_kv: int = 0):
+    """The same for token rows that each stand alone: row t is request seq_of_token[t] at position positions[t].
+    `max_kv` (a bound on any row's position + 1; 0: unknown) lets rows with many visible keys be cut into runs that
+    several blocks share."""
     return _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, None, None, seq_of_token, positions, scale,
                              window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, tokens, 1,
-                             tokens, out)
+                             tokens, out, max_kv=max_kv)
 
 
 def embedding_pair(ids, positions, seq_of_token, cu_seqlens, state_slots, last_token: torch.Tensor,

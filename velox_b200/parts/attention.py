@@ -176,7 +176,7 @@ class PagedAttention(Mixer):
                 return ops.biased_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                                    ctx.seq_of_token, ctx.positions, self.scale, self.window,
                                                    self.keep_first, self.bias_exponent, H, Hk, D, self.v_head_dim,
-                                                   qkv.shape[0])
+                                                   qkv.shape[0], max_kv=ctx.max_kv)
             return ops.biased_prefill_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                                 ctx.cu_seqlens, ctx.kv_offsets, self.scale, self.window, self.keep_first,
                                                 self.bias_exponent, H, Hk, D, self.v_head_dim, ctx.n_seqs, ctx.max_new,
