@@ -39,12 +39,12 @@ def config(vocab, width, layers, residual_mult=0.5, eps=1e-5, buckets=53, mul_pr
             "layers": layers}
 
 
-# odd sizes everywhere: nothing a fast kernel takes; every kind of feed-forward; values of the size of keys in
+# odd sizes everywhere (one layer's heads of 27, 11 and 7 elements): nothing a fast kernel takes; every kind of feed-forward; values of the size of keys in
 # one layer; one key/value head per query head in one layer; a window longer than any test sequence; an expert
 # size that is no multiple of 8; as many chosen experts as there are; no shared expert; a decay of exactly 1
-ODD = config(97, 76, [
+ODD = config(97, 140, [
     layer(left(4, 2, 16, 8, 0.3, 9, 2), right(2, 8, 16, [0.9, 0.5]), moe(12, 3, 1)),
-    layer(left(2, 2, 32, 32, 0.2, 5, 0), right(3, 12, 8, [1.0, 0.8, 0.25]), None),
+    layer(left(2, 2, 27, 27, 0.2, 5, 0), right(3, 11, 7, [1.0, 0.8, 0.25]), None),
     layer(left(6, 1, 16, 24, 0.25, 17, 3), right(1, 20, 40, [0.97]), {"kind": "dense", "ff": 40}),
     layer(left(4, 4, 8, 12, 0.5, 400, 1), right(2, 16, 16, [0.6, 0.99]), moe(16, 4, 4, shared=24)),
 ])

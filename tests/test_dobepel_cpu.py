@@ -16,7 +16,7 @@ def test_the_configuration_reads_every_size_from_the_file_and_writes_it_back():
     raw = copy.deepcopy(CONFIGS["odd"])
     assert resolve_architecture(raw).name == "Dobepel"
     cfg = DobepelConfig.from_dict(raw)
-    assert (cfg.vocab, cfg.width, cfg.residual_mult, cfg.norm_eps) == (97, 76, 0.5, 1e-5)
+    assert (cfg.vocab, cfg.width, cfg.residual_mult, cfg.norm_eps) == (97, 140, 0.5, 1e-5)
     assert (cfg.bigram_buckets, cfg.bigram_mul_prev, cfg.bigram_mul_cur) == (53, 31, 7)
     assert DobepelConfig.from_dict(json.loads(json.dumps(cfg.to_dict()))) == cfg
     faults = copy.deepcopy(raw)

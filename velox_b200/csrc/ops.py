@@ -281,10 +281,9 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
           "paged_attention: int32 block table [requests, blocks]")
     _need(k_pool.dtype == q.dtype and v_pool.dtype == q.dtype, "paged_attention: pools of the queries' element type")
-    _need(attention_head_dim_supported(head_dim),
-          "paged_attention: head size %d (the kernels take even sizes up to %d)" % (head_dim, ATTENTION_MAX_HEAD_DIM))
-    _need(attention_head_dim_supported(v_head_dim) or v_head_dim == head_dim,
-          "paged_attention: value size %d (the kernels take even sizes up to %d)" % (v_head_dim, ATTENTION_MAX_HEAD_DIM))
+    _need(0 < head_dim <= ATTENTION_MAX_HEAD_DIM and 0 < v_head_dim <= ATTENTION_MAX_HEAD_DIM,
+          "paged_attention: head sizes %d / %d (the general kernel takes sizes up to %d)"
+          % (head_dim, v_head_dim, ATTENTION_MAX_HEAD_DIM))
     out = torch.empty((tokens, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
     _check(library().vx_paged_attention_generic(
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],

@@ -63,7 +63,8 @@ class PagedAttention(Mixer):
         self.names = dict(zip(("q_proj", "k_proj", "v_proj", "o_proj"), names))
         if num_heads % num_kv_heads:
             raise ValueError("num_heads %d is not a multiple of num_kv_heads %d" % (num_heads, num_kv_heads))
-        if not ops.attention_head_dim_supported(int(head_dim)):
+        plain = position is None and not qk_norm   # (no rotation, no norm: the general kernel takes odd sizes too)
+        if not (ops.attention_head_dim_supported(int(head_dim)) or (plain and 0 < int(head_dim) <= ops.ATTENTION_MAX_HEAD_DIM)):
             raise ValueError("%shead_dim %d: the attention kernels take even head sizes up to %d"
                              % (prefix, head_dim, ops.ATTENTION_MAX_HEAD_DIM))
         self.v_head_dim = int(v_head_dim) or int(head_dim)
@@ -72,8 +73,8 @@ class PagedAttention(Mixer):
             raise ValueError("%skeep_first and distance_bias_exponent must not be negative" % prefix)
         if self.v_head_dim != int(head_dim) and (qk_norm or position is not None or bias):
             raise ValueError("%svalues of another size than keys go with plain projections (no q/k norm, rotation, bias)" % prefix)
-        if not ops.attention_head_dim_supported(self.v_head_dim):
-            raise ValueError("%sv_head_dim %d: the attention kernels take even sizes up to %d"
+        if not 0 < self.v_head_dim <= ops.ATTENTION_MAX_HEAD_DIM:
+            raise ValueError("%sv_head_dim %d: the attention kernels take sizes up to %d"
                              % (prefix, self.v_head_dim, ops.ATTENTION_MAX_HEAD_DIM))
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.head_dim, self.bias, self.qk_norm = int(head_dim), bool(bias), bool(qk_norm)
@@ -142,7 +143,8 @@ class PagedAttention(Mixer):
         group = ctx.groups[cache.group]
         qkv = self.qkv(h)
         slots = group.slot_mapping if cache.writes else None
-        if self.v_head_dim != D:
+        if self.extended and not self.qk_norm and self.position is None:
+            # plain projections: nothing to norm or rotate, the step's keys and values go into their pages as they are
             if slots is not None:
                 ops.kv_store(qkv, H * D, (H + Hk) * D, slots, cache.k_pool, cache.v_pool)
             return self.out(self._attend_extended(qkv, ctx, cache, group))
