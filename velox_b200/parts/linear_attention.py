@@ -4,9 +4,12 @@ The heads' outputs are joined, RMS-normed over their whole width with a weight, 
 and projected by W_o.  There is no other scale and no position encoding.
 
 The state is float32, starts at zero and lives in the request's state slot (`FixedState`), so a step runs
-only the tokens it brings.  The four input projections are one matrix here ([W_q; W_k; W_v; W_g]); the
-activation of q, k, v is taken in float32 inside the recurrence kernel, which reads them from the packed
-projection.  Decays, state, outputs, the norm and the gate are float32.
+only the tokens it brings.  The four input projections are one matrix here ([W_q; W_k; W_v; W_g]).  Three
+kernels share the work (`ops.linear_attention`, `csrc/linear_attention.cu`): the recurrence token by token
+(decode steps, short portions, float32), chunks of 64 tokens on the tensor cores one after the other, and, for
+portions of 256 tokens or more, all chunks side by side with a scan between them.  The activation of q, k, v
+is taken in float32 (rounded to bfloat16 in a bfloat16 engine, the same way by every kernel).  Decays, state,
+outputs, the norm and the gate are float32.
 """
 from __future__ import annotations
 
