@@ -168,7 +168,8 @@ def assert_close(got, want, dtype, what="", cost=None, judge=None):
                              % (what, int(bad.sum()), FP32_ATOL, idx, got[idx], want[idx], rows[0], rows[:20].tolist()))
 
 
-def run_trace(model_dir, dtype, steps, max_tokens, out_dir, page_size=16, poison=True, timeout=600, max_requests=None):
+def run_trace(model_dir, dtype, steps, max_tokens, out_dir, page_size=16, poison=True, timeout=600, max_requests=None,
+              vocab=None):
     """Runs bin/trace_run as a user would: steps on stdin one at a time, waiting
     for `done <step>` after each.  Returns {step: float32 array [wanted, vocab]}."""
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
@@ -189,8 +190,9 @@ def run_trace(model_dir, dtype, steps, max_tokens, out_dir, page_size=16, poison
     finally:
         if proc.poll() is None:
             proc.kill()
-    with open(os.path.join(model_dir, "config.json")) as f:
-        vocab = json.load(f)["vocab_size"]
+    if vocab is None:
+        with open(os.path.join(model_dir, "config.json")) as f:
+            vocab = json.load(f)["vocab_size"]
     out = {}
     for rec in steps:
         p = os.path.join(out_dir, "%s.f32" % rec["step"])

@@ -215,3 +215,36 @@ def test_the_command_line_writes_and_runs_a_random_model(tmp_path):
                           "--prompt-tokens", "5,6,7,8", "--max-tokens", "4", "--dtype", "float32"],
                          cwd=root, capture_output=True, text=True)
     assert gen.returncode == 0, gen.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_trace_runner_replays_requests_through_four_slots(models, tmp_path, dtype):
+    """bin/trace_run as a user starts it (its own process, four state slots, a pool of 24 pages): five requests, at most
+    four of them live, portions beside single tokens, a request left out of steps, slots and pages used again."""
+    from helpers import run_trace
+    cfg, w, folder = models["even" if dtype == "float32" else "dense"]
+    toks = {k: tokens_of(cfg, n, 60 + i) for i, (k, n) in enumerate({"p": 100, "q": 37, "r": 64, "s": 2, "t": 90}.items())}
+    oracle = {k: Oracle(cfg, w, t) for k, t in toks.items()}
+    at = {k: 0 for k in toks}
+    steps, expect = [], []
+
+    def step(parts, end=()):
+        entries, rows = [], []
+        for k, n in parts:
+            lo, hi = at[k], min(at[k] + n, len(toks[k]))
+            at[k] = hi
+            entries.append({"id": k, "tokens": toks[k][lo:hi], "want": list(range(hi - lo))})
+            rows.append((oracle[k], lo, hi))
+        steps.append({"step": len(steps), "entries": entries, "end": list(end)})
+        expect.append(rows)
+    step([("p", 40), ("q", 36), ("r", 1)])
+    step([("p", 1), ("q", 1), ("r", 63), ("s", 2)], end=["q", "r", "s"])
+    step([("t", 33)])                          # ("p" is left out of this step)
+    step([("p", 59), ("t", 1)], end=["p"])
+    step([("t", 56)], end=["t"])
+    got = run_trace(folder, dtype, steps, 24 * 16, str(tmp_path / "out"), vocab=cfg["vocab"])
+    judge = RoundingJudge.of(oracle.values(), "dobepel trace runner %s" % dtype)
+    for n, rows in enumerate(expect):
+        compare(got[n], rows, dtype, "step %d" % n, judge)
+    if dtype != "float32":
+        judge.finish()
