@@ -705,11 +705,24 @@ __global__ void linear_attention_scan_kernel(const float* __restrict__ decay, fl
     const float log2d = log2f(decay[h]);
     float* st = state + ((size_t)state_slots[seq] * H + h) * cells + e;
     float run = *st;
-    for (int c = 0, left = len; left > 0; ++c, left -= LC_CHUNK) {
-        float* p = scratch + ((size_t)(first + c) * H + h) * cells + e;
-        const float u = *p;
-        *p = run;
-        run = fmaf(exp2f((float)min(LC_CHUNK, left) * log2d), run, u);
+    const int nchunks = (len + LC_CHUNK - 1) / LC_CHUNK;
+    const size_t stride = (size_t)H * cells;
+    float* p0 = scratch + ((size_t)first * H + h) * cells + e;
+    const float full = exp2f((float)LC_CHUNK * log2d);
+    // eight chunks' contributions are asked for at once (read one by one, each costs a memory latency: 33 chunks
+    // took 50 us), then the chain of multiply-adds runs over them
+    for (int c0 = 0; c0 < nchunks; c0 += 8) {
+        float u[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) u[j] = c0 + j < nchunks ? p0[(size_t)(c0 + j) * stride] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (c0 + j < nchunks) {
+                p0[(size_t)(c0 + j) * stride] = run;
+                const int n = min(LC_CHUNK, len - (c0 + j) * LC_CHUNK);
+                run = fmaf(n == LC_CHUNK ? full : exp2f((float)n * log2d), run, u[j]);
+            }
+        }
     }
     *st = run;
 }

@@ -318,11 +318,43 @@ __global__ void act_kernel(const TI* __restrict__ x, int ldx, TO* __restrict__ o
     }
 }
 
+// The same, 8 elements a thread and access (width and row stride multiples of 8, 16-byte aligned pointers).
+template <typename TI, typename TO>
+__global__ void act_vec_kernel(const TI* __restrict__ x, int ldx, TO* __restrict__ out, long long chunks, int row_chunks,
+                               int act) {
+    pdl_wait();
+    pdl_trigger();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / row_chunks;
+        const int c = (int)(i - r * row_chunks) * 8;
+        float v[8];
+        mn_load8(x + r * ldx + c, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = activation(v[j], act);
+        mn_store8(out + i * 8, v);
+    }
+}
+
 extern "C" int vx_act(const void* x, int ldx, void* out, int rows, int width, int act, int in_dtype, int out_dtype,
                       cudaStream_t stream) {
     if (rows <= 0 || width <= 0) return VX_OK;
     if (ldx < width || act < 0 || act > 3) return VX_ERR_SHAPE;
     const long long total = (long long)rows * width;
+    if (width % 8 == 0 && ldx % 8 == 0 && !((((uintptr_t)x) | ((uintptr_t)out)) & 15)) {
+        const long long chunks = total / 8;
+        long long vb = (chunks + 255) / 256;
+        if (vb > 148 * 16) vb = 148 * 16;
+        if (in_dtype == VX_F32 && out_dtype == VX_F32)
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (act_vec_kernel<float, float>), (int)vb, 256, 0, stream, (const float*)x, ldx, (float*)out, chunks, width / 8, act);
+        else if (in_dtype == VX_BF16 && out_dtype == VX_BF16)
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (act_vec_kernel<bf16, bf16>), (int)vb, 256, 0, stream, (const bf16*)x, ldx, (bf16*)out, chunks, width / 8, act);
+        else if (in_dtype == VX_F32 && out_dtype == VX_BF16)
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (act_vec_kernel<float, bf16>), (int)vb, 256, 0, stream, (const float*)x, ldx, (bf16*)out, chunks, width / 8, act);
+        else
+            return VX_ERR_DTYPE;
+        VX_LAUNCH_CHECK();
+        return VX_OK;
+    }
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (in_dtype == VX_F32 && out_dtype == VX_F32)
