@@ -291,3 +291,144 @@ class DobepelConfig(ModelConfig):
                     positive(at + ".mlp.shared", mlp["shared"], "ff")
         if faults:
             raise ConfigError("Dobepel configuration: " + "; ".join(faults))
+
+
+@dataclass(frozen=True)
+class BuvuzenConfig(ModelConfig):
+    """Buvuzen: a decoder whose config.json is nested and lists its layers one by one.
+
+        architecture   "Buvuzen"
+        vocab, width, norm.eps, embedding.scale, logit_scale
+        layers[i]      type ("attention"),
+                       mixer (heads, kv_heads, dim, vdim, scale, mask.size),
+                       mlp: null | kind "moe" (expert.ff, router.experts, router.identity, router.top, router.scale,
+                       router.groups.count, router.groups.keep, shared.ff or no shared),
+                       weights_of: j (optional): the layer has no tensors of its own and runs with layer j's
+
+    Every size and constant is read from there; the layers may differ from one another.  Absent optional keys mean
+    "not there": no window (mask), multipliers of 1, no identity experts, one group, no shared expert."""
+
+    architecture: ClassVar[str] = "Buvuzen"
+    model_type: ClassVar[str] = "buvuzen"
+    LAYER_TYPES: ClassVar[Tuple[str, ...]] = ("attention",)
+
+    vocab: int = _field(int)
+    width: int = _field(int)
+    norm_eps: float = _field(float)
+    embedding_scale: float = _field(float, default=1.0)
+    logit_scale: float = _field(float, default=1.0)
+    layers: Tuple[Dict[str, Any], ...] = _field(tuple, default=())
+
+    @classmethod
+    def from_dict(cls, raw: Dict[str, Any]) -> "BuvuzenConfig":
+        faults: list = []
+
+        def get(d, path, kind, default=dataclasses.MISSING):
+            cur = d
+            for key in path.split("."):
+                if not isinstance(cur, dict) or cur.get(key) is None:
+                    if default is dataclasses.MISSING:
+                        faults.append("missing key %r" % path)
+                    return None if default is dataclasses.MISSING else default
+                cur = cur[key]
+            return _typed(path, cur, kind, faults)
+
+        values = dict(vocab=get(raw, "vocab", int), width=get(raw, "width", int), norm_eps=get(raw, "norm.eps", float),
+                      embedding_scale=get(raw, "embedding.scale", float, 1.0), logit_scale=get(raw, "logit_scale", float, 1.0))
+        layers = raw.get("layers")
+        if not isinstance(layers, list) or not layers:
+            faults.append("key 'layers': expected a list of layers")
+            layers = []
+        if faults:
+            raise ConfigError("config.json for %s: %s" % (cls.__name__, "; ".join(faults)))
+        cfg = cls(layers=tuple(json.loads(json.dumps(layer)) for layer in layers), **values)
+        cfg.validate()
+        return cfg
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"architecture": self.architecture, "embedding": {"scale": self.embedding_scale},
+                "layers": json.loads(json.dumps(list(self.layers))), "logit_scale": self.logit_scale,
+                "norm": {"eps": self.norm_eps}, "vocab": self.vocab, "width": self.width}
+
+    def weights_layer(self, i: int) -> int:
+        """The layer whose tensors layer i runs with: itself, or the end of its `weights_of` chain."""
+        seen = set()
+        while self.layers[i].get("weights_of") is not None:
+            seen.add(i)
+            i = int(self.layers[i]["weights_of"])
+            if i in seen:
+                raise ConfigError("Buvuzen configuration: the layers' weights_of form a circle at layer %d" % i)
+        return i
+
+    def validate(self) -> None:
+        faults = []
+
+        def positive(where, d, *keys):
+            for k in keys:
+                v = d.get(k) if isinstance(d, dict) else None
+                if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+                    faults.append("%s.%s must be a positive integer, got %r" % (where, k, v))
+                    return False
+            return True
+
+        def count(where, d, key, default, least=0):
+            v = d.get(key, default) if isinstance(d, dict) else default
+            if v is None:
+                v = default
+            if not isinstance(v, int) or isinstance(v, bool) or v < least:
+                faults.append("%s.%s must be an integer >= %d, got %r" % (where, key, least, v))
+                return default
+            return v
+
+        def number(where, d, key):
+            v = d.get(key, 1.0) if isinstance(d, dict) else None
+            if not isinstance(v, (int, float)) or isinstance(v, bool):
+                faults.append("%s.%s must be a number, got %r" % (where, key, v))
+
+        for name in ("vocab", "width"):
+            if getattr(self, name) <= 0:
+                faults.append("%s must be positive, got %d" % (name, getattr(self, name)))
+        if not self.norm_eps > 0:
+            faults.append("norm.eps must be positive, got %r" % self.norm_eps)
+        n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            at = "layers[%d]" % i
+            if not isinstance(layer, dict) or layer.get("type") not in self.LAYER_TYPES:
+                faults.append("%s.type %r is not one of %s" % (at, layer.get("type") if isinstance(layer, dict) else layer,
+                                                               list(self.LAYER_TYPES)))
+                continue
+            j = layer.get("weights_of")
+            if j is not None and (not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < n or j == i):
+                faults.append("%s.weights_of must name another layer, got %r" % (at, j))
+            mixer = layer.get("mixer")
+            if positive(at + ".mixer", mixer, "heads", "kv_heads", "dim", "vdim"):
+                if mixer["heads"] % mixer["kv_heads"]:
+                    faults.append("%s.mixer: heads (%d) is not a multiple of kv_heads (%d)" % (at, mixer["heads"], mixer["kv_heads"]))
+                if "scale" not in mixer:
+                    faults.append("%s.mixer.scale is missing" % at)
+                number(at + ".mixer", mixer, "scale")
+                count(at + ".mixer.mask", mixer.get("mask") or {}, "size", 0)
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if not isinstance(mlp, dict) or mlp.get("kind") != "moe":
+                faults.append("%s.mlp.kind %r is not 'moe'" % (at, mlp.get("kind") if isinstance(mlp, dict) else mlp))
+                continue
+            positive(at + ".mlp.expert", mlp.get("expert"), "ff")
+            router = mlp.get("router")
+            if positive(at + ".mlp.router", router, "experts", "top"):
+                outputs = router["experts"] + count(at + ".mlp.router", router, "identity", 0)
+                groups = router.get("groups") or {}
+                g, keep = count(at + ".mlp.router.groups", groups, "count", 1, 1), count(at + ".mlp.router.groups", groups, "keep", 1, 1)
+                number(at + ".mlp.router", router, "scale")
+                if outputs % g or keep > g:
+                    faults.append("%s.mlp.router: %d outputs do not form %d equal groups of which %d are kept" % (at, outputs, g, keep))
+                elif router["top"] > keep * (outputs // g):
+                    faults.append("%s.mlp.router: top (%d) exceeds the outputs of the kept groups (%d)"
+                                  % (at, router["top"], keep * (outputs // g)))
+            if mlp.get("shared") is not None:
+                positive(at + ".mlp.shared", mlp["shared"], "ff")
+        if faults:
+            raise ConfigError("Buvuzen configuration: " + "; ".join(faults))
+        for i in range(n):
+            self.weights_layer(i)

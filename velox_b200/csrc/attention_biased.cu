@@ -4,6 +4,9 @@
 //   score(i, j) = q_i . k_j * scale - slope_h * (i - j),   slope_h = 2^(-bias_exp * (h + 1) / H)
 //   query i sees key j  iff  j <= i and (window == 0 or i - j < window or j < keep_first)
 //   keys of size DK (64, 128), values of size DV (32, 64, 128), which need not be equal
+//   optionally a sink per query head: the softmax's denominator also holds exp(sinks[h]) (no key, no value,
+//   not scaled), and an output gate: head h's output times sigmoid(g), g the element at column
+//   gate_col + h of the token's row of `q`
 //
 // Portions: grid (query tile, head, segment); 4 warps.  A segment is a request's portion of this step
 // (rows cu_seqlens[s] .. of positions kv_offsets[s] ..).  A step of single tokens has a kernel of its
@@ -35,6 +38,21 @@ template <int CH> __device__ __forceinline__ int ab_swz(int r, int cc) {
     return CH >= 8 ? (cc ^ (r & 7)) : (cc ^ ((r >> 1) & 3));
 }
 
+// The sink's share of a row's softmax: the denominator l (relative to the maximum m, base 2) gains
+// 2^(sink - m); where the sink exceeds m the reference moves to the sink and `f` scales what was summed.
+__device__ __forceinline__ void ab_add_sink(float sink_log2, float m, float& l, float& f) {
+    f = 1.f;
+    if (sink_log2 > m) {
+        f = exp2f(m - sink_log2);
+        l = l * f + 1.f;
+    } else {
+        l += exp2f(sink_log2 - m);
+    }
+}
+__device__ __forceinline__ float ab_gate(const bf16* q, int q_row_stride, int row, int gate_col, int head) {
+    return 1.f / (1.f + __expf(-__bfloat162float(q[(size_t)row * q_row_stride + gate_col + head])));
+}
+
 struct AbSegments {
     const int* cu_seqlens;    // portions: rows of segment s are [cu_seqlens[s], cu_seqlens[s + 1])
     const int* kv_offsets;    //           at positions kv_offsets[s] ..
@@ -47,7 +65,8 @@ __global__ void __launch_bounds__(AB_WARPS * 32)
 biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ k_pool,
                         const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
                         AbSegments seg, bf16* __restrict__ out, int out_row_stride, float scale_log2, float bias_exp,
-                        int window, int keep_first, int H, int Hk, int S, int share_log2) {
+                        int window, int keep_first, int H, int Hk, int S, int share_log2,
+                        const float* __restrict__ sinks, int gate_col) {
     extern __shared__ __align__(128) unsigned char ab_smem[];
     constexpr int KCH = DK / 8, VCH = DV / 8;
     constexpr int K_BYTES = AB_BN * DK * 2, V_BYTES = AB_BN * DV * 2;
@@ -286,7 +305,10 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
         const int tok = r >> share_log2;
         if (tok >= toks_live) continue;
         const int hd = head0 + (r & (share - 1));
-        const float inv = 1.f / l[hrow];
+        float f = 1.f;
+        if (sinks) ab_add_sink(sinks[hd] * AB_LOG2E, m[hrow], l[hrow], f);
+        if (gate_col >= 0) f *= ab_gate(q, q_row_stride, row_base + t0 + tok, gate_col, hd);
+        const float inv = f / l[hrow];
         bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)hd * DV + ((lane & 3) << 1);
 #pragma unroll
         for (int nt = 0; nt < DV / 8; ++nt)
@@ -309,7 +331,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
                      const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
                      const int* __restrict__ seq_of_token, const int* __restrict__ positions, bf16* __restrict__ out,
                      int out_row_stride, float scale_log2, float bias_exp, int window, int keep_first, int H, int Hk,
-                     int S, int share_log2, float* __restrict__ scratch) {
+                     int S, int share_log2, float* __restrict__ scratch, const float* __restrict__ sinks, int gate_col) {
     extern __shared__ __align__(128) unsigned char ad_smem[];
     constexpr int KCH = DK / 8, VCH = DV / 8;
     constexpr int K_BYTES = 16 * DK * 2, V_BYTES = 16 * DV * 2;
@@ -489,7 +511,10 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
             acc += p[d] * f;
         }
         if (gridDim.z == 1) {
-            out[(size_t)t * out_row_stride + (size_t)(head0 + r) * DV + d] = __float2bfloat16_rn(acc / L);
+            float f = 1.f;
+            if (sinks) ab_add_sink(sinks[head0 + r] * AB_LOG2E, M, L, f);
+            if (gate_col >= 0) f *= ab_gate(q, q_row_stride, t, gate_col, head0 + r);
+            out[(size_t)t * out_row_stride + (size_t)(head0 + r) * DV + d] = __float2bfloat16_rn(acc * f / L);
         } else {
             float* dst = scratch + (((size_t)t * H + head0 + r) * gridDim.z + blockIdx.z) * (DV + 2);
             dst[d] = acc;
@@ -500,7 +525,8 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
 
 // The runs' parts of one (token, head), added in order: out = sum_z acc_z 2^(M_z - M) / sum_z L_z 2^(M_z - M).
 __global__ void biased_decode_join_kernel(const float* __restrict__ scratch, bf16* __restrict__ out, int out_row_stride,
-                                          int H, int DV, int runs) {
+                                          int H, int DV, int runs, const float* __restrict__ sinks,
+                                          const bf16* __restrict__ qrows, int q_row_stride, int gate_col) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x, h = blockIdx.y;
@@ -515,7 +541,10 @@ __global__ void biased_decode_join_kernel(const float* __restrict__ scratch, bf1
             L += q[DV + 1] * f;
             acc += q[d] * f;
         }
-        out[(size_t)t * out_row_stride + (size_t)h * DV + d] = __float2bfloat16_rn(acc / L);
+        float f = 1.f;
+        if (sinks) ab_add_sink(sinks[h] * AB_LOG2E, M, L, f);
+        if (gate_col >= 0) f *= ab_gate(qrows, q_row_stride, t, gate_col, h);
+        out[(size_t)t * out_row_stride + (size_t)h * DV + d] = __float2bfloat16_rn(acc * f / L);
     }
 }
 
@@ -523,7 +552,8 @@ template <int DK, int DV>
 static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool,
                                 const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
                                 bf16* out, int out_row_stride, float scale, float bias_exp, int window, int keep_first,
-                                int tokens, int H, int Hk, int S, float* scratch, int runs, cudaStream_t stream) {
+                                int tokens, int H, int Hk, int S, float* scratch, int runs, const float* sinks, int gate_col,
+                                cudaStream_t stream) {
     const size_t walk = (size_t)AD_WARPS * 2 * (16 * DK * 2 + 16 * DV * 2), parts = (size_t)AD_WARPS * 16 * (DV + 2) * 4;
     const size_t smem = 16 * DK * 2 + (walk > parts ? walk : parts);
     static bool configured[VX_MAX_DEVICES];
@@ -536,10 +566,10 @@ static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_p
     dim3 grid(share_log2 ? Hk : H, tokens, runs);
     VX_LAUNCH_K(VX_K_ATTENTION, (biased_decode_kernel<DK, DV>), grid, AD_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
                 v_pool, block_table, max_blocks, seq_of_token, positions, out, out_row_stride, scale * AB_LOG2E, bias_exp,
-                window, keep_first, H, Hk, S, share_log2, scratch);
+                window, keep_first, H, Hk, S, share_log2, scratch, sinks, gate_col);
     if (runs > 1)
         VX_LAUNCH_K(VX_K_JOIN, biased_decode_join_kernel, dim3(tokens, H), DV >= 128 ? 128 : 64, 0, stream, (const float*)scratch,
-                    out, out_row_stride, H, DV, runs);
+                    out, out_row_stride, H, DV, runs, sinks, q, q_row_stride, gate_col);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -547,7 +577,8 @@ static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_p
 template <int DK, int DV>
 static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
                          int max_blocks, AbSegments seg, bf16* out, int out_row_stride, float scale, float bias_exp,
-                         int window, int keep_first, int segments, int max_new, int H, int Hk, int S, cudaStream_t stream) {
+                         int window, int keep_first, int segments, int max_new, int H, int Hk, int S, const float* sinks,
+                         int gate_col, cudaStream_t stream) {
     const size_t smem = (size_t)AB_BM * DK * 2 + 2 * ((size_t)AB_BN * DK * 2 + (size_t)AB_BN * DV * 2);
     static bool configured[VX_MAX_DEVICES];
     if (int rc = vx_configure_smem(biased_attention_kernel<DK, DV>, smem, configured)) return rc;
@@ -559,7 +590,7 @@ static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, co
     dim3 grid((max_new + toks_per_tile - 1) / toks_per_tile, share_log2 ? Hk : H, segments);
     VX_LAUNCH_K(VX_K_ATTENTION, (biased_attention_kernel<DK, DV>), grid, AB_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
                 v_pool, block_table, max_blocks, seg, out, out_row_stride, scale * AB_LOG2E, bias_exp, window, keep_first, H,
-                Hk, S, share_log2);
+                Hk, S, share_log2, sinks, gate_col);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -571,7 +602,8 @@ extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* 
                                    const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
                                    const int* seq_of_token, const int* positions, void* out, int out_row_stride,
                                    float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
-                                   int H, int Hk, int DK, int DV, int S, float* scratch, int runs, cudaStream_t stream) {
+                                   int H, int Hk, int DK, int DV, int S, float* scratch, int runs, const float* sinks,
+                                   int gate_col, cudaStream_t stream) {
     if (segments <= 0 || max_new <= 0) return VX_OK;
     if (H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
     if (cu_seqlens ? !kv_offsets : (!seq_of_token || !positions || max_new != 1)) return VX_ERR_SHAPE;
@@ -583,7 +615,8 @@ extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* 
     if (DK == K_ && DV == V_)                                                                                               \
         return launch_biased_decode<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,       \
                                             block_table, max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, \
-                                            scale, bias_exp, window, keep_first, segments, H, Hk, S, scratch, runs, stream)
+                                            scale, bias_exp, window, keep_first, segments, H, Hk, S, scratch, runs, sinks,  \
+                                            gate_col, stream)
         AD_GO(64, 32); AD_GO(64, 64); AD_GO(64, 128); AD_GO(128, 32); AD_GO(128, 64); AD_GO(128, 128);
 #undef AD_GO
         return VX_ERR_SHAPE;
@@ -593,7 +626,7 @@ extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* 
     if (DK == K_ && DV == V_)                                                                                             \
         return launch_biased<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, \
                                      max_blocks, seg, (bf16*)out, out_row_stride, scale, bias_exp, window, keep_first,    \
-                                     segments, max_new, H, Hk, S, stream)
+                                     segments, max_new, H, Hk, S, sinks, gate_col, stream)
     AB_GO(64, 32); AB_GO(64, 64); AB_GO(64, 128); AB_GO(128, 32); AB_GO(128, 64); AB_GO(128, 128);
 #undef AB_GO
     return VX_ERR_SHAPE;

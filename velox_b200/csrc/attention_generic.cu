@@ -11,6 +11,10 @@
 // j % S; pools are [page, Hk, S, D] and [page, Hk, S, Dv]; query head h reads kv head
 // h / (H / Hk).  score = q.k * scale - slope_h * (p - j) with
 // slope_h = 2^(-bias_exp * (h + 1) / H), or no bias for bias_exp = 0.
+// With `sinks` (a float32 per query head) the softmax's denominator also holds
+// exp(sinks[h]): an entry without a key or a value, not scaled.  With gate_col >= 0
+// head h's output is multiplied by sigmoid(g), g the element at column gate_col + h
+// of the token's row of `q`.
 //
 // Each warp takes chunks of 32 keys (chunk c goes to warp c mod 4), one key per
 // lane: the lane forms the whole dot product q.k in float32, the warp keeps a
@@ -30,7 +34,7 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, T* __restrict__ out,
     int out_row_stride, float scale, int window, int H, int Hk, int D, int S, int Dv, int keep_first,
-    float bias_exp) {
+    float bias_exp, const float* __restrict__ sinks, int gate_col) {
     pdl_wait();
     pdl_trigger();
     __shared__ float q_s[ATT_MAX_D];
@@ -108,10 +112,23 @@ __global__ void paged_attention_generic_kernel(
         wgt[w] = (m_s[w] == -INFINITY) ? 0.f : expf(m_s[w] - M);
         L += l_s[w] * wgt[w];
     }
+    if (sinks) {
+        // the sink joins the denominator only; where it exceeds every score the reference moves to it
+        const float sk = sinks[h];
+        if (sk > M) {
+            const float f = expf(M - sk);   // (M is finite: a token always sees itself)
+            L = L * f + 1.f;
+            for (int w = 0; w < ATT_WARPS; ++w) wgt[w] *= f;
+        } else {
+            L += expf(sk - M);
+        }
+    }
+    float gate = 1.f;
+    if (gate_col >= 0) gate = 1.f / (1.f + expf(-to_f32(q[(size_t)t * q_row_stride + gate_col + h])));
     for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < ATT_WARPS; ++w) o += acc_s[w][d] * wgt[w];
-        out[(size_t)t * out_row_stride + (size_t)h * Dv + d] = from_f32<T>(o / L);
+        out[(size_t)t * out_row_stride + (size_t)h * Dv + d] = from_f32<T>(o / L * gate);
     }
 }
 
@@ -120,7 +137,7 @@ extern "C" int vx_paged_attention_generic(const void* q, int q_row_stride, const
                                           const int* seq_of_token, const int* positions, void* out,
                                           int out_row_stride, float scale, int window, int tokens,
                                           int H, int Hk, int D, int S, int dtype, int Dv, int keep_first,
-                                          float bias_exp, cudaStream_t stream) {
+                                          float bias_exp, const float* sinks, int gate_col, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
     if (Dv <= 0) Dv = D;
     if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > ATT_MAX_D || Dv > ATT_MAX_D || S <= 0 || max_blocks <= 0)
@@ -129,10 +146,10 @@ extern "C" int vx_paged_attention_generic(const void* q, int q_row_stride, const
     dim3 grid(tokens, H);
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<float>), grid, ATT_WARPS * 32, 0, stream, (const float*)q, q_row_stride, (const float*)k_pool, (const float*)v_pool, block_table,
-            max_blocks, seq_of_token, positions, (float*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp);
+            max_blocks, seq_of_token, positions, (float*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col);
     else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<bf16>), grid, ATT_WARPS * 32, 0, stream, (const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-            max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp);
+            max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

@@ -186,6 +186,7 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 #define VX_ACT_GELU 1
 #define VX_ACT_GELU_TANH 2
 #define VX_ACT_RELU 3
+#define VX_ACT_IDENTITY 4   // (a plain change of element type through the activation kernel)
 
 __device__ __forceinline__ float activation(float z, int act) {
     switch (act) {
@@ -195,6 +196,7 @@ __device__ __forceinline__ float activation(float z, int act) {
             const float c = 0.7978845608028654f;
             return 0.5f * z * (1.f + tanhf(c * (z + 0.044715f * z * z * z)));
         }
+        case VX_ACT_IDENTITY: return z;
         default: return fmaxf(z, 0.f);
     }
 }

@@ -6,12 +6,14 @@
 // matrix product are rounded to T.
 #include "common.cuh"
 
-// out[t, :] = table[ids[t], :] widened to float32.  An id outside [0, vocab)
+// out[t, :] = table[ids[t], :] widened to float32 and multiplied by `scale`; `rounded`
+// (optional) takes the same rows in the table's element type, for a first sublayer that
+// reads the stream itself.  An id outside [0, vocab)
 // yields a row of NaN: the host checks ids before a step, and a fault in that
 // check then shows in every comparison instead of reading foreign memory.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int hidden, int vocab) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale, T* __restrict__ rounded) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
@@ -22,18 +24,22 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
         return;
     }
     const T* row = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float x = to_f32(row[i]) * scale;
+        o[i] = x;
+        if (rounded) rounded[(size_t)t * hidden + i] = from_f32<T>(x);
+    }
 }
 
 extern "C" int vx_embedding(const int* ids, const void* table, float* out, int tokens, int hidden,
-                            int vocab, int dtype, cudaStream_t stream) {
+                            int vocab, int dtype, float scale, void* rounded, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
     if (hidden <= 0 || vocab <= 0) return VX_ERR_SHAPE;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (embedding_kernel<float>), tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (embedding_kernel<float>), tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab, scale, (float*)rounded);
     else if (dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (embedding_kernel<bf16>), tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (embedding_kernel<bf16>), tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab, scale, (bf16*)rounded);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
@@ -334,28 +340,29 @@ extern "C" int vx_gated_act(const void* gate_up, void* out, int rows, int inner,
     return VX_ERR_DTYPE;
 }
 
-// out[m, n] = in[m, n] + bias[n], float32 in, float32 or bfloat16 out: the bias of a
-// library product is added to its float32 sums, and the result rounded once.
+// out[m, n] = (in[m, n] + bias[n]) * scale, float32 in, float32 or bfloat16 out: the bias of a
+// library product is added to its float32 sums, and the result rounded once.  Without a bias
+// only the multiplier is applied (a head whose logits are scaled).
 template <typename TO>
 __global__ void add_bias_kernel(const float* __restrict__ in, const float* __restrict__ bias, TO* __restrict__ out,
-                                long long total, int n) {
+                                long long total, int n, float scale) {
     pdl_wait();
     pdl_trigger();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x)
-        out[idx] = from_f32<TO>(in[idx] + bias[idx % n]);
+        out[idx] = from_f32<TO>((in[idx] + (bias ? bias[idx % n] : 0.f)) * scale);
 }
 
 extern "C" int vx_add_bias(const float* in, const float* bias, void* out, int rows, int n, int out_dtype,
-                           cudaStream_t stream) {
+                           float scale, cudaStream_t stream) {
     if (rows <= 0 || n <= 0) return VX_OK;
     const long long total = (long long)rows * n;
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     if (out_dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_bias_kernel<float>), (int)blocks, 256, 0, stream, in, bias, (float*)out, total, n);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_bias_kernel<float>), (int)blocks, 256, 0, stream, in, bias, (float*)out, total, n, scale);
     else if (out_dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_bias_kernel<bf16>), (int)blocks, 256, 0, stream, in, bias, (bf16*)out, total, n);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_bias_kernel<bf16>), (int)blocks, 256, 0, stream, in, bias, (bf16*)out, total, n, scale);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

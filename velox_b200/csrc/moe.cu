@@ -1,14 +1,20 @@
 // A routed feed-forward (mixture of experts) without a trip to the host:
 //
 //   route     per token: logits = W_r h + b in float32, the `top` largest (lowest index first
-//             among equals), softmax over the chosen logits only; counts the tokens of every expert
+//             among equals), softmax over the chosen logits only; counts the tokens of every expert.
+//             Or (mode 1) scores s = softmax(logits) over ALL outputs, choice by s + correction among the
+//             outputs of the best `keep_groups` of `groups` equal groups of neighbours (a group's score:
+//             its largest choice score), weights s * route_scale, not renormalised.  The router's last
+//             outputs may be identity experts (no matrices: the token itself), and one more row of the
+//             router's matrix may hold the gate of a shared expert, sigmoid(w . h) per token
 //   plan      one block: where each expert's rows start in expert order, the list of row tiles
 //             (expert, first row, rows) that the grouped products walk, and for every
 //             assignment (token, k) its row in expert order
 //   grouped product   C[p, :] = A[src(p), :] W_e^T for the rows p of each tile, W = [experts, N, K];
 //             optionally with act(gate) * up on the accumulators (W's rows in tiles of 8 gate rows
 //             followed by their 8 up rows)
-//   combine   out[t] = sum_k weight[t, k] * y[row of (t, k)] (+ shared[t]) in float32, k ascending
+//   combine   out[t] = sum_k weight[t, k] * y[row of (t, k)] (+ gate[t] * shared[t]) in float32, k ascending;
+//             an assignment to an identity expert adds weight * h[t] instead
 //
 // The grid of a grouped product is sized for the worst case (assignments / tile rows + experts
 // tiles); blocks beyond the step's real number of tiles leave at once.  Which tile a row falls
@@ -36,9 +42,14 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_router, const float* __restrict__ bias,
                  int tokens, int K, int E, int top, int* __restrict__ chosen, float* __restrict__ weight,
-                 int* __restrict__ counts, int* __restrict__ pos, int vec) {
-    __shared__ float z_s[4][MOE_MAX_EXPERTS];
+                 int* __restrict__ counts, int* __restrict__ pos, int vec, int mode, const float* __restrict__ correction,
+                 int groups, int keep_groups, float route_scale, float* __restrict__ shared_gate) {
+    __shared__ float z_s[4][MOE_MAX_EXPERTS + 8];
     __shared__ float zc_s[4][MOE_MAX_TOP];
+    __shared__ float sc_s[4][MOE_MAX_EXPERTS];      // mode 1: the scores of all outputs
+    __shared__ float gs_s[4][MOE_MAX_EXPERTS];      //         the groups' scores
+    __shared__ unsigned char kept_s[4][MOE_MAX_EXPERTS];
+    const int rows = E + (shared_gate ? 1 : 0);     // rows of the router's matrix: the outputs, then the shared gate's
     pdl_wait();
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -51,7 +62,7 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
         // memory with every thread's loads in flight at once (read one after the other by a single warp they cost a
         // memory latency each: 25 us for 8 experts of 2,048), then each warp takes its token's 8 dot products from there.
         __shared__ __align__(16) float w_s[8][ROUTE_KC];
-        for (int e0 = 0; e0 < E; e0 += 8) {
+        for (int e0 = 0; e0 < rows; e0 += 8) {
             float acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -63,7 +74,7 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
                     const int idx = threadIdx.x + u * 128;
                     const int e = idx / (ROUTE_KC / 4), c = (idx % (ROUTE_KC / 4)) * 4;
                     v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (k0 + c < K) v[u] = *reinterpret_cast<const float4*>(w_router + (size_t)min(e0 + e, E - 1) * K + k0 + c);
+                    if (k0 + c < K) v[u] = *reinterpret_cast<const float4*>(w_router + (size_t)min(e0 + e, rows - 1) * K + k0 + c);
                 }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
@@ -90,20 +101,67 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float s = warp_sum(acc[j]);
-                if (lane == 0 && e0 + j < E) z[e0 + j] = s + (bias ? bias[e0 + j] : 0.f);
+                if (lane == 0 && e0 + j < rows) z[e0 + j] = s + ((bias && e0 + j < E) ? bias[e0 + j] : 0.f);
             }
         }
     } else if (valid) {
-        for (int e = 0; e < E; ++e) {
+        for (int e = 0; e < rows; ++e) {
             const float* w = w_router + (size_t)e * K;
             float s = 0.f;
             for (int k = lane; k < K; k += 32) s = fmaf(to_f32(row[k]), w[k], s);
             s = warp_sum(s);
-            if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+            if (lane == 0) z[e] = s + ((bias && e < E) ? bias[e] : 0.f);
         }
     }
     if (!valid) return;
     __syncwarp();
+    if (shared_gate && lane == 0) shared_gate[t] = 1.f / (1.f + expf(-z[E]));
+    float* sc = sc_s[warp];
+    if (mode == 1) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - mx); sc[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) {
+            const float v = sc[e] / sum;
+            sc[e] = v;
+            z[e] = v + (correction ? correction[e] : 0.f);   // the choice score; the weight stays v
+        }
+        __syncwarp();
+        if (groups > 1 && keep_groups < groups) {
+            const int gsize = E / groups;
+            float* gs = gs_s[warp];
+            unsigned char* kept = kept_s[warp];
+            for (int g = lane; g < groups; g += 32) {
+                float b = -INFINITY;
+                for (int e = g * gsize; e < (g + 1) * gsize; ++e) b = fmaxf(b, z[e]);
+                gs[g] = b;
+                kept[g] = 0;
+            }
+            __syncwarp();
+            for (int i = 0; i < keep_groups; ++i) {
+                float best = -INFINITY;
+                int arg = 0x7fffffff;
+                for (int g = lane; g < groups; g += 32) {
+                    const float v = gs[g];
+                    if (!kept[g] && (v > best || (v == best && g < arg))) { best = v; arg = g; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                    if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+                }
+                if (lane == 0 && arg != 0x7fffffff) kept[arg] = 1;
+                __syncwarp();
+            }
+            for (int e = lane; e < E; e += 32)
+                if (!kept[e / gsize]) z[e] = -INFINITY;   // (not 0: a choice score may be negative)
+            __syncwarp();
+        }
+    }
     for (int i = 0; i < top; ++i) {
         float best = -INFINITY;
         int arg = 0x7fffffff;
@@ -118,14 +176,16 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
         if (lane == 0) {
-            zc_s[warp][i] = best;
+            zc_s[warp][i] = mode == 1 ? sc[arg] : best;
             z[arg] = -INFINITY;
             chosen[(size_t)t * top + i] = arg;
             pos[(size_t)t * top + i] = atomicAdd(&counts[arg], 1);
         }
         __syncwarp();
     }
-    if (lane == 0) {
+    if (lane == 0 && mode == 1) {
+        for (int i = 0; i < top; ++i) weight[(size_t)t * top + i] = zc_s[warp][i] * route_scale;
+    } else if (lane == 0) {
         const float m = zc_s[warp][0];
         float sum = 0.f;
         for (int i = 0; i < top; ++i) sum += expf(zc_s[warp][i] - m);
@@ -137,7 +197,7 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ chosen, const int* __restrict__ pos, int* __restrict__ counts, int assignments,
                 int E, int tile_rows, int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ n_tiles,
-                int* __restrict__ src_of_row, int* __restrict__ row_of) {
+                int* __restrict__ src_of_row, int* __restrict__ row_of, int tile_experts) {
     __shared__ int off_s[MOE_MAX_EXPERTS + 1];
     pdl_wait();
     pdl_trigger();
@@ -147,7 +207,8 @@ moe_plan_kernel(const int* __restrict__ chosen, const int* __restrict__ pos, int
             off_s[e] = run;
             offsets[e] = run;
             const int c = counts[e];
-            for (int r = 0; r < c; r += tile_rows) {
+            // (outputs from `tile_experts` on are identity experts: their rows keep a place, no product walks them)
+            for (int r = 0; r < c && e < tile_experts; r += tile_rows) {
                 tiles[3 * n] = e;
                 tiles[3 * n + 1] = run + r;
                 tiles[3 * n + 2] = min(tile_rows, c - r);
@@ -169,25 +230,35 @@ moe_plan_kernel(const int* __restrict__ chosen, const int* __restrict__ pos, int
     for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;   // ready for the next step
 }
 
+// E: the router's outputs (experts, then `identity` identity experts).  mode 0: top-k of the logits, softmax over
+// the chosen; mode 1: softmax over all, choice by score + correction within the best groups, weights score * route_scale.
+// With `shared_gate` the router's matrix has one more row and shared_gate[t] = sigmoid(that row . h[t]).
 extern "C" int vx_moe_route(const void* h, int ldh, const float* w_router, const float* bias, int tokens, int K, int E,
                             int top, int tile_rows, int* chosen, float* weight, int* counts, int* pos, int* offsets,
-                            int* tiles, int* n_tiles, int* src_of_row, int* row_of, int dtype, cudaStream_t stream) {
+                            int* tiles, int* n_tiles, int* src_of_row, int* row_of, int dtype, int mode,
+                            const float* correction, int groups, int keep_groups, float route_scale, int identity,
+                            float* shared_gate, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
     if (K <= 0 || E <= 0 || top <= 0 || top > E || tile_rows <= 0) return VX_ERR_SHAPE;
+    if (mode < 0 || mode > 1 || identity < 0 || identity >= E) return VX_ERR_SHAPE;
+    if (groups < 1) groups = 1;
+    if (E % groups || keep_groups < 1 || keep_groups > groups || top > keep_groups * (E / groups)) return VX_ERR_SHAPE;
     if (E > MOE_MAX_EXPERTS || top > MOE_MAX_TOP) return VX_ERR_LIMIT;
     const int blocks = (tokens + 3) / 4;
     const int elt = dtype == VX_F32 ? 4 : 2;
     const int vec = K % 8 == 0 && (ldh * elt) % 16 == 0 && !(((uintptr_t)h) & 15) && !(((uintptr_t)w_router) & 15);
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_route_kernel<float>), blocks, 128, 0, stream, (const float*)h, ldh, w_router, bias,
-                    tokens, K, E, top, chosen, weight, counts, pos, vec);
+                    tokens, K, E, top, chosen, weight, counts, pos, vec, mode, correction, groups, keep_groups, route_scale,
+                    shared_gate);
     else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_route_kernel<bf16>), blocks, 128, 0, stream, (const bf16*)h, ldh, w_router, bias,
-                    tokens, K, E, top, chosen, weight, counts, pos, vec);
+                    tokens, K, E, top, chosen, weight, counts, pos, vec, mode, correction, groups, keep_groups, route_scale,
+                    shared_gate);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_K(VX_K_ELEMENTWISE, moe_plan_kernel, 1, 1024, 0, stream, (const int*)chosen, (const int*)pos, counts,
-                tokens * top, E, tile_rows, offsets, tiles, n_tiles, src_of_row, row_of);
+                tokens * top, E, tile_rows, offsets, tiles, n_tiles, src_of_row, row_of, E - identity);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -564,41 +635,49 @@ extern "C" int vx_moe_gather_rows(const void* x, int ldx, const int* src_of_row,
 template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ row_of,
                                    const float* __restrict__ weight, const T* __restrict__ shared_out,
-                                   T* __restrict__ out, int width, int top) {
+                                   T* __restrict__ out, int width, int top, const int* __restrict__ chosen, int n_real,
+                                   const T* __restrict__ h, int ldh, const float* __restrict__ shared_gate) {
     __shared__ int row_s[MOE_MAX_TOP];
     __shared__ float w_s[MOE_MAX_TOP];
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
     if (threadIdx.x < top) {
-        row_s[threadIdx.x] = row_of[(size_t)t * top + threadIdx.x];
+        // (a negative row: the assignment went to an identity expert, whose output is the token's own row)
+        const bool same = chosen && chosen[(size_t)t * top + threadIdx.x] >= n_real;
+        row_s[threadIdx.x] = same ? -1 : row_of[(size_t)t * top + threadIdx.x];
         w_s[threadIdx.x] = weight[(size_t)t * top + threadIdx.x];
     }
     __syncthreads();
+    const float g = shared_gate ? shared_gate[t] : 1.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k) s = fmaf(w_s[k], to_f32(y[(size_t)row_s[k] * width + i]), s);
-        if (shared_out) s += to_f32(shared_out[(size_t)t * width + i]);
+        for (int k = 0; k < top; ++k)
+            s = fmaf(w_s[k], row_s[k] < 0 ? to_f32(h[(size_t)t * ldh + i]) : to_f32(y[(size_t)row_s[k] * width + i]), s);
+        if (shared_out) s = fmaf(g, to_f32(shared_out[(size_t)t * width + i]), s);
         out[(size_t)t * width + i] = from_f32<T>(s);
     }
 }
 
 // y_dtype: the element type of the experts' rows (float32, or bfloat16 from the tcgen05 product).
+// With `chosen` and `n_real`, assignments to outputs >= n_real take the token's own row of `h` [tokens, ldh] instead of
+// a row of `y`; with `shared_gate` the shared expert's row is multiplied by shared_gate[t].
 extern "C" int vx_moe_combine(const void* y, const int* row_of, const float* weight, const void* shared_out, void* out,
-                              int tokens, int width, int top, int dtype, int y_dtype, cudaStream_t stream) {
+                              int tokens, int width, int top, int dtype, int y_dtype, const int* chosen, int n_real,
+                              const void* h, int ldh, const float* shared_gate, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
-    if (width <= 0 || top <= 0) return VX_ERR_SHAPE;
+    if (width <= 0 || top <= 0 || (chosen && !h)) return VX_ERR_SHAPE;
     if (top > MOE_MAX_TOP) return VX_ERR_LIMIT;
     const int threads = width >= 1024 ? 256 : 128;
     if (dtype == VX_F32 && y_dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<float, float>), tokens, threads, 0, stream, (const float*)y, row_of,
-                    weight, (const float*)shared_out, (float*)out, width, top);
+                    weight, (const float*)shared_out, (float*)out, width, top, chosen, n_real, (const float*)h, ldh, shared_gate);
     else if (dtype == VX_BF16 && y_dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<bf16, float>), tokens, threads, 0, stream, (const float*)y, row_of,
-                    weight, (const bf16*)shared_out, (bf16*)out, width, top);
+                    weight, (const bf16*)shared_out, (bf16*)out, width, top, chosen, n_real, (const bf16*)h, ldh, shared_gate);
     else if (dtype == VX_BF16 && y_dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_combine_kernel<bf16, bf16>), tokens, threads, 0, stream, (const bf16*)y, row_of,
-                    weight, (const bf16*)shared_out, (bf16*)out, width, top);
+                    weight, (const bf16*)shared_out, (bf16*)out, width, top, chosen, n_real, (const bf16*)h, ldh, shared_gate);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

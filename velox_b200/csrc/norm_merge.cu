@@ -72,6 +72,7 @@ extern "C" int vx_embedding_pair(const int* ids, const int* positions, const int
 //   u = c0 * rms(y0) * w0 + c1 * rms(y1) * w1     two branches, each normed over the row
 //   r = residual + mult * rms(u) * w_post    stored back into residual
 //   out = rms(r) * w_next                    if w_next is given
+//   out = r rounded to T                     if `out` is given without w_next (a next sublayer that reads the stream itself)
 // Without w_post (and without a residual) out = u: the merged branches alone.
 // The row of u (then r) is kept in shared memory between the passes; every thread
 // re-reads only what it wrote itself.
@@ -125,7 +126,11 @@ __global__ void merge_norm_add_norm_kernel(float* __restrict__ residual, const T
         row[i] = r;
         sr += r * r;
     }
-    if (!w_next) return;
+    if (!w_next) {
+        if (out)
+            for (int i = threadIdx.x; i < width; i += blockDim.x) out[base + i] = from_f32<T>(row[i]);
+        return;
+    }
     sr = block_sum(sr, scratch);
     const float rr = rsqrtf(sr * inv + eps);
     for (int i = threadIdx.x; i < width; i += blockDim.x) out[base + i] = from_f32<T>(row[i] * rr * w_next[i]);
@@ -248,6 +253,7 @@ merge_norm_add_norm_vec_kernel(float* __restrict__ residual, const T* __restrict
                 sr += r[i][j] * r[i][j];
             }
             mn_store8(residual + base + c * 8, r[i]);
+            if (out && !w_next) mn_store8(out + base + c * 8, r[i]);
         }
     }
     if (!w_next) return;
@@ -338,7 +344,7 @@ __global__ void act_vec_kernel(const TI* __restrict__ x, int ldx, TO* __restrict
 extern "C" int vx_act(const void* x, int ldx, void* out, int rows, int width, int act, int in_dtype, int out_dtype,
                       cudaStream_t stream) {
     if (rows <= 0 || width <= 0) return VX_OK;
-    if (ldx < width || act < 0 || act > 3) return VX_ERR_SHAPE;
+    if (ldx < width || act < 0 || act > VX_ACT_IDENTITY) return VX_ERR_SHAPE;
     const long long total = (long long)rows * width;
     if (width % 8 == 0 && ldx % 8 == 0 && !((((uintptr_t)x) | ((uintptr_t)out)) & 15)) {
         const long long chunks = total / 8;

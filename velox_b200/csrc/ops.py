@@ -21,6 +21,7 @@ _LIB = None
 
 VX_F32, VX_BF16 = 0, 1
 ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "relu": 3}
+_ACT_IDENTITY = 4   # (the activation kernel as a plain change of element type)
 _ERRORS = {
     -1: "a size the kernel does not take",
     -2: "an element type the kernel does not know",
@@ -64,14 +65,14 @@ def is_loaded() -> bool:
 def _declare(lib) -> None:
     P, I, F = c_void_p, c_int, c_float
     sigs = {
-        "vx_embedding": [P, P, P, I, I, I, I, P],
+        "vx_embedding": [P, P, P, I, I, I, I, F, P, P],
         "vx_add_rmsnorm": [P, P, P, P, P, P, I, I, F, I, P],
         "vx_rmsnorm": [P, P, P, I, I, F, I, P],
         "vx_gated_act": [P, P, I, I, I, I, I, I, P],
-        "vx_add_bias": [P, P, P, I, I, I, P],
-        "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
-        "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, I, I, F, P],
-        "vx_biased_attention": [P, I, P, P, P, I, P, P, P, P, P, I, F, F, I, I, I, I, I, I, I, I, I, P, I, P],
+        "vx_add_bias": [P, P, P, I, I, I, F, P],
+        "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, I, P],
+        "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, I, I, F, P, I, P],
+        "vx_biased_attention": [P, I, P, P, P, I, P, P, P, P, P, I, F, F, I, I, I, I, I, I, I, I, I, P, I, P, I, P],
         "vx_embedding_pair": [P, P, P, P, P, P, P, P, P, I, I, I, I, c_longlong, c_longlong, I, P],
         "vx_merge_norm_add_norm": [P, P, P, F, P, P, F, P, F, P, P, I, I, F, I, P],
         "vx_act": [P, I, P, I, I, I, I, I, P],
@@ -80,9 +81,9 @@ def _declare(lib) -> None:
         "vx_linear_attention_recurrent": [P, I, I, I, I, P, P, P, P, P, I, I, I, I, I, I, P],
         "vx_linear_attention_chunked": [P, I, I, I, I, P, P, P, P, P, I, I, I, I, P],
         "vx_linear_attention_parallel": [P, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P],
-        "vx_moe_route": [P, I, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, P],
+        "vx_moe_route": [P, I, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P, P, I, I, P, I, I, F, I, P, P],
         "vx_moe_gemm": [P, I, P, I, P, P, P, I, P, I, I, I, I, I, I, I, I, I, P],
-        "vx_moe_combine": [P, P, P, P, P, I, I, I, I, I, P],
+        "vx_moe_combine": [P, P, P, P, P, I, I, I, I, I, P, I, P, I, P, P],
         "vx_moe_gather_rows": [P, I, P, I, P, I, I, P],
         "vx_moe_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, P, P, I, P, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
@@ -165,15 +166,20 @@ def _dev(*tensors) -> None:
 
 
 # ----------------------------------------------------------------------------
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """float32 rows of `table` [V,E] at int32 `ids` [T]."""
-    _dev(ids, table)
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0,
+              rounded: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 rows of `table` [V,E] at int32 `ids` [T], times `scale`; `rounded` [T,E] (the table's element
+    type) takes the same rows rounded."""
+    _dev(ids, table, rounded)
     _need(ids.dtype == torch.int32 and ids.is_contiguous() and table.is_contiguous(), "embedding: int32 ids, contiguous")
     t, (v, e) = ids.numel(), table.shape
     if out is None:
         out = torch.empty((t, e), dtype=torch.float32, device=table.device)
-    _check(library().vx_embedding(_ptr(ids), _ptr(table), _ptr(out), t, e, v, dtype_code(table.dtype), _stream()),
-           "embedding")
+    if rounded is not None:
+        _need(rounded.dtype == table.dtype and rounded.is_contiguous() and tuple(rounded.shape) == (t, e),
+              "embedding: the rounded copy has the table's element type and the result's shape")
+    _check(library().vx_embedding(_ptr(ids), _ptr(table), _ptr(out), t, e, v, dtype_code(table.dtype), float(scale),
+                                  _ptr(rounded), _stream()), "embedding")
     return out
 
 
@@ -238,16 +244,19 @@ def gated_act(gate_up: torch.Tensor, activation: str, block: int = 0,
 
 def qk_norm_rope_kv(qkv: torch.Tensor, q_weight, k_weight, eps: float, inv_freq, rot_dim: int,
                     positions: torch.Tensor, slot_mapping, k_pool, v_pool, num_heads: int, num_kv_heads: int,
-                    head_dim: int) -> None:
-    """In place on the packed projections `qkv` [T, (H+2Hk)D]; writes new keys
-    and values into the pools [pages, Hk, S, D] when a slot mapping is given."""
+                    head_dim: int, v_head_dim: int = 0) -> None:
+    """In place on the packed projections `qkv` [T, (H+Hk)D + Hk Dv (+ more)]; writes new keys
+    and values into the pools [pages, Hk, S, D] and [pages, Hk, S, Dv] when a slot mapping is given
+    (`v_head_dim` 0: values of the keys' size)."""
+    v_head_dim = int(v_head_dim) or head_dim
     _dev(qkv, q_weight, k_weight, inv_freq, positions, slot_mapping, k_pool, v_pool)
     _need(qkv.is_contiguous() and positions.dtype == torch.int32, "qk_norm_rope_kv: contiguous qkv, int32 positions")
     page_size = 1
     if slot_mapping is not None:
         _need(k_pool is not None and v_pool is not None and k_pool.dtype == qkv.dtype and k_pool.is_contiguous()
               and v_pool.is_contiguous(), "qk_norm_rope_kv: pools of the activations' element type")
-        _need(tuple(k_pool.shape[1:]) == (num_kv_heads, k_pool.shape[2], head_dim), "qk_norm_rope_kv: pool shape")
+        _need(tuple(k_pool.shape[1:]) == (num_kv_heads, k_pool.shape[2], head_dim)
+              and tuple(v_pool.shape[1:]) == (num_kv_heads, k_pool.shape[2], v_head_dim), "qk_norm_rope_kv: pool shape")
         page_size = k_pool.shape[2]
     if inv_freq is not None:
         _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dim, "qk_norm_rope_kv: inv_freq size")
@@ -257,7 +266,7 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_weight, k_weight, eps: float, inv_freq,
     _check(library().vx_qk_norm_rope_kv(
         _ptr(qkv), qkv.shape[-1], _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), int(rot_dim),
         _ptr(positions), _ptr(slot_mapping), _ptr(k_pool), _ptr(v_pool), qkv.shape[0], num_heads, num_kv_heads,
-        head_dim, page_size, dtype_code(qkv.dtype), _stream()), "qk_norm_rope_kv")
+        head_dim, page_size, dtype_code(qkv.dtype), v_head_dim, _stream()), "qk_norm_rope_kv")
 
 
 ATTENTION_MAX_HEAD_DIM = 256
@@ -272,11 +281,14 @@ def attention_head_dim_supported(head_dim: int) -> bool:
 def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
                             seq_of_token, positions, scale: float, window: int, num_heads: int,
                             num_kv_heads: int, head_dim: int, tokens: int, v_head_dim: int = 0, keep_first: int = 0,
-                            bias_exponent: float = 0.0) -> torch.Tensor:
+                            bias_exponent: float = 0.0, sinks: Optional[torch.Tensor] = None,
+                            gate_col: int = -1) -> torch.Tensor:
     """The general kernel.  `v_head_dim`: size of a value (0: a key's); `keep_first`: with a window, the
     first positions that stay visible; `bias_exponent` b > 0: head h's scores lose
-    2^(-b (h + 1) / heads) * distance."""
-    _dev(q, k_pool, v_pool, block_table, seq_of_token, positions)
+    2^(-b (h + 1) / heads) * distance; `sinks` (float32 per head): the softmax's denominator also holds
+    exp(sink); `gate_col` >= 0: head h's output times sigmoid of column gate_col + h of the token's row of `q`."""
+    _dev(q, k_pool, v_pool, block_table, seq_of_token, positions, sinks)
+    _check_sinks_gate("paged_attention", sinks, gate_col, num_heads, q_row_stride)
     v_head_dim = int(v_head_dim) or head_dim
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
           "paged_attention: int32 block table [requests, blocks]")
@@ -289,8 +301,15 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
         _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * v_head_dim, float(scale), int(window), tokens,
         num_heads, num_kv_heads, head_dim, k_pool.shape[2], dtype_code(q.dtype), v_head_dim, int(keep_first),
-        float(bias_exponent), _stream()), "paged_attention_generic")
+        float(bias_exponent), _ptr(sinks), int(gate_col), _stream()), "paged_attention_generic")
     return out
+
+
+def _check_sinks_gate(what: str, sinks, gate_col: int, num_heads: int, q_row_stride: int) -> None:
+    if sinks is not None:
+        _need(sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_heads,
+              "%s: one float32 sink per query head" % what)
+    _need(gate_col < 0 or gate_col + num_heads <= q_row_stride, "%s: the gates' columns lie outside the row" % what)
 
 
 BIASED_DECODE_MAX_RUNS = 8
@@ -304,8 +323,9 @@ def biased_attention_supported(dtype, head_dim: int, v_head_dim: int, page_size:
 
 def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions,
                       scale, window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, segments,
-                      max_new, tokens, out, max_kv=0):
-    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions, out)
+                      max_new, tokens, out, max_kv=0, sinks=None, gate_col=-1):
+    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions, out, sinks)
+    _check_sinks_gate("biased_attention", sinks, gate_col, num_heads, q_row_stride)
     _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
           "biased_attention: bfloat16 only")
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
@@ -325,30 +345,33 @@ def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, 
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(cu_seqlens),
         _ptr(kv_offsets), _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * v_head_dim, float(scale),
         float(bias_exponent), int(window), int(keep_first), int(segments), int(max_new), num_heads, num_kv_heads, head_dim,
-        v_head_dim, k_pool.shape[2], _ptr(scratch), runs, _stream()), "biased_attention")
+        v_head_dim, k_pool.shape[2], _ptr(scratch), runs, _ptr(sinks), int(gate_col), _stream()), "biased_attention")
     return out
 
 
 def biased_prefill_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, scale: float,
                              window: int, keep_first: int, bias_exponent: float, num_heads: int, num_kv_heads: int,
-                             head_dim: int, v_head_dim: int, requests: int, max_new: int, tokens: int, out=None):
+                             head_dim: int, v_head_dim: int, requests: int, max_new: int, tokens: int, out=None,
+                             sinks=None, gate_col: int = -1):
     """Attention of prompt portions (request i: rows cu_seqlens[i] .. at positions kv_offsets[i] ..) with
     score = q.k * scale - 2^(-bias_exponent (h+1) / heads) * distance under a window that keeps the first
-    `keep_first` positions; bfloat16, tensor cores, probabilities in two bfloat16 halves."""
+    `keep_first` positions; bfloat16, tensor cores, probabilities in two bfloat16 halves.  `sinks` and `gate_col`
+    as in `paged_attention_generic`."""
     return _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, None, None, scale,
                              window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, requests,
-                             max_new, tokens, out)
+                             max_new, tokens, out, sinks=sinks, gate_col=gate_col)
 
 
 def biased_decode_attention(q, q_row_stride, k_pool, v_pool, block_table, seq_of_token, positions, scale: float,
                             window: int, keep_first: int, bias_exponent: float, num_heads: int, num_kv_heads: int,
-                            head_dim: int, v_head_dim: int, tokens: int, out=None, max_kv: int = 0):
+                            head_dim: int, v_head_dim: int, tokens: int, out=None, max_kv: int = 0, sinks=None,
+                            gate_col: int = -1):
     """The same for token rows that each stand alone: row t is request seq_of_token[t] at position positions[t].
     `max_kv` (a bound on any row's position + 1; 0: unknown) lets rows with many visible keys be cut into runs that
     several blocks share."""
     return _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, None, None, seq_of_token, positions, scale,
                              window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, tokens, 1,
-                             tokens, out, max_kv=max_kv)
+                             tokens, out, max_kv=max_kv, sinks=sinks, gate_col=gate_col)
 
 
 def embedding_pair(ids, positions, seq_of_token, cu_seqlens, state_slots, last_token: torch.Tensor,
@@ -370,10 +393,11 @@ def embedding_pair(ids, positions, seq_of_token, cu_seqlens, state_slots, last_t
 
 
 def merge_norm_add_norm(residual: torch.Tensor, y0: torch.Tensor, w_post: torch.Tensor, mult: float, eps: float,
-                        w0=None, c0: float = 1.0, y1=None, w1=None, c1: float = 1.0, w_next=None):
+                        w0=None, c0: float = 1.0, y1=None, w1=None, c1: float = 1.0, w_next=None, rounded: bool = False):
     """residual (float32, in place) += mult * rmsnorm(u) * w_post, with u = y0, or with two branches
     u = c0 rmsnorm(y0) w0 + c1 rmsnorm(y1) w1.  Returns rmsnorm(residual) * w_next in y0's element type
-    if `w_next` is given, else None."""
+    if `w_next` is given; with `rounded` the new residual itself in y0's element type (for a next sublayer
+    that reads the stream without a norm before it); else None."""
     _dev(residual, y0, w_post, w0, y1, w1, w_next)
     _need(residual.dtype == torch.float32 and residual.is_contiguous() and y0.is_contiguous()
           and y0.shape == residual.shape, "merge_norm_add_norm: float32 residual, a branch of its shape")
@@ -384,7 +408,8 @@ def merge_norm_add_norm(residual: torch.Tensor, y0: torch.Tensor, w_post: torch.
     if y1 is not None:
         _need(y1.is_contiguous() and y1.shape == y0.shape and y1.dtype == y0.dtype and w0 is not None and w1 is not None,
               "merge_norm_add_norm: two branches of one shape, each with its weight")
-    out = torch.empty_like(y0) if w_next is not None else None
+    _need(not (rounded and w_next is not None), "merge_norm_add_norm: the next norm or the rounded stream, not both")
+    out = torch.empty_like(y0) if (w_next is not None or rounded) else None
     _check(library().vx_merge_norm_add_norm(_ptr(residual), _ptr(y0), _ptr(w0), float(c0), _ptr(y1), _ptr(w1), float(c1),
                                             _ptr(w_post), float(mult), _ptr(w_next), _ptr(out), residual.shape[0], width,
                                             float(eps), dtype_code(y0.dtype), _stream()), "merge_norm_add_norm")
@@ -414,6 +439,25 @@ def act(x: torch.Tensor, activation: str, out_dtype: Optional[torch.dtype] = Non
     out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
     _check(library().vx_act(_ptr(x), x.stride(0), _ptr(out), x.shape[0], x.shape[1], ACTIVATIONS[activation],
                             dtype_code(x.dtype), dtype_code(out.dtype), _stream()), "act")
+    return out
+
+
+def cast_rows(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x [rows, width] (contiguous rows) in another element type, rounded to nearest."""
+    _dev(x)
+    _need(x.dim() == 2 and x.stride(1) == 1, "cast_rows: rows must be contiguous")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _check(library().vx_act(_ptr(x), x.stride(0), _ptr(out), x.shape[0], x.shape[1], _ACT_IDENTITY,
+                            dtype_code(x.dtype), dtype_code(out.dtype), _stream()), "cast_rows")
+    return out
+
+
+def scale_rows(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """float32 x [rows, n] times a number."""
+    _dev(x)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "scale_rows: float32 rows")
+    out = torch.empty_like(x)
+    _check(library().vx_add_bias(_ptr(x), None, _ptr(out), x.shape[0], x.shape[1], VX_F32, float(scale), _stream()), "scale_rows")
     return out
 
 
@@ -513,25 +557,38 @@ MOE_TCGEN05_MIN_ROWS = 1024   # assignments of a step from which the tcgen05 gro
 class MoePlan:
     """What `moe_route` leaves on the device for the grouped products and the combination."""
     __slots__ = ("chosen", "weight", "tiles", "n_tiles", "src_of_row", "row_of", "max_tiles", "top", "assignments",
-                 "tile_rows", "experts")
+                 "tile_rows", "experts", "identity", "shared_gate")
 
 
 _MOE_COUNTS = {}
 
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias, experts: int, top: int,
-              tile_rows: int = MOE_TILE_ROWS) -> MoePlan:
+              tile_rows: int = MOE_TILE_ROWS, scores: str = "softmax_chosen", correction=None, groups: int = 1,
+              keep_groups: int = 1, route_scale: float = 1.0, identity: int = 0, shared_gate: bool = False) -> MoePlan:
     """Router logits in float32, the `top` largest per token, softmax over the chosen; then every
-    assignment's row in expert order and the row tiles (of up to `tile_rows` rows) of the grouped products."""
-    _dev(h, w_router, bias)
+    assignment's row in expert order and the row tiles (of up to `tile_rows` rows) of the grouped products.
+
+    `experts` counts the router's outputs.  `scores="softmax_all"`: scores s = softmax over all outputs, choice by
+    s + `correction` (float32 per output) among the outputs of the `keep_groups` best of `groups` equal groups of
+    neighbours, weights s * route_scale (not renormalised).  The last `identity` outputs are identity experts (the
+    combination takes the token's own row for them).  With `shared_gate` the router's matrix has one more row, and
+    `plan.shared_gate` [tokens] is sigmoid(that row . h)."""
+    _dev(h, w_router, bias, correction)
+    rows = experts + (1 if shared_gate else 0)
     _need(h.stride(1) == 1 and w_router.dtype == torch.float32 and w_router.is_contiguous()
-          and tuple(w_router.shape) == (experts, h.shape[1]), "moe_route: float32 router [experts, width]")
-    if bias is not None:
-        _need(bias.dtype == torch.float32 and bias.numel() == experts, "moe_route: float32 bias per expert")
+          and tuple(w_router.shape) == (rows, h.shape[1]), "moe_route: float32 router [outputs (+ 1 for a shared gate), width]")
+    _need(scores in ("softmax_chosen", "softmax_all"), "moe_route: scores %r" % (scores,))
+    _need(groups >= 1 and experts % groups == 0 and 1 <= keep_groups <= groups and top <= keep_groups * (experts // groups)
+          and 0 <= identity < experts, "moe_route: groups, kept groups, top and identity experts do not fit the outputs")
+    for b in (bias, correction):
+        if b is not None:
+            _need(b.dtype == torch.float32 and b.numel() == experts, "moe_route: float32 bias / correction per output")
     t, dev = h.shape[0], h.device
     a = t * top
     plan = MoePlan()
-    plan.top, plan.assignments, plan.tile_rows, plan.experts = top, a, int(tile_rows), experts
+    plan.top, plan.assignments, plan.tile_rows, plan.experts, plan.identity = top, a, int(tile_rows), experts, int(identity)
+    plan.shared_gate = torch.empty(t, dtype=torch.float32, device=dev) if shared_gate else None
     plan.max_tiles = -(-a // plan.tile_rows) + experts
     ints = torch.empty(3 * a + (experts + 1) + 3 * plan.max_tiles + 1 + a, dtype=torch.int32, device=dev)
     plan.chosen, pos, plan.src_of_row, plan.row_of = ints[:a], ints[a:2 * a], ints[2 * a:3 * a], ints[3 * a:4 * a]
@@ -547,7 +604,9 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias, experts: int, top: 
     _check(library().vx_moe_route(_ptr(h), h.stride(0), _ptr(w_router), _ptr(bias), t, h.shape[1], experts, top,
                                   plan.tile_rows, _ptr(plan.chosen), _ptr(plan.weight), _ptr(counts), _ptr(pos), _ptr(offsets),
                                   _ptr(plan.tiles), _ptr(plan.n_tiles), _ptr(plan.src_of_row), _ptr(plan.row_of),
-                                  dtype_code(h.dtype), _stream()), "moe_route")
+                                  dtype_code(h.dtype), 1 if scores == "softmax_all" else 0, _ptr(correction), int(groups),
+                                  int(keep_groups), float(route_scale), int(identity), _ptr(plan.shared_gate), _stream()),
+           "moe_route")
     return plan
 
 
@@ -617,10 +676,14 @@ def moe_gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gated_acti
     return out
 
 
-def moe_combine(y: torch.Tensor, plan: MoePlan, shared_out, out_dtype: torch.dtype) -> torch.Tensor:
+def moe_combine(y: torch.Tensor, plan: MoePlan, shared_out, out_dtype: torch.dtype, h=None) -> torch.Tensor:
     """Per token the weighted sum of its experts' rows of `y` (expert order; float32, or the result's element
-    type), plus `shared_out`."""
-    _dev(y, shared_out)
+    type), plus `shared_out` (times the plan's shared gate, if it has one).  A plan with identity experts needs
+    `h`, the tokens' rows that went into the router: an assignment to one of them adds weight * h[t]."""
+    _dev(y, shared_out, h)
+    if plan.identity:
+        _need(h is not None and h.dtype == out_dtype and h.stride(1) == 1 and h.shape[1] == y.shape[1],
+              "moe_combine: identity experts take the tokens' own rows, in the result's element type")
     _need(y.dtype in (torch.float32, out_dtype) and y.is_contiguous(), "moe_combine: float32 rows, or rows of the result's type")
     t = plan.assignments // plan.top
     if shared_out is not None:
@@ -628,7 +691,10 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, shared_out, out_dtype: torch.dty
               "moe_combine: the shared expert's output in the result's shape and element type")
     out = torch.empty((t, y.shape[1]), dtype=out_dtype, device=y.device)
     _check(library().vx_moe_combine(_ptr(y), _ptr(plan.row_of), _ptr(plan.weight), _ptr(shared_out), _ptr(out), t, y.shape[1],
-                                    plan.top, dtype_code(out_dtype), dtype_code(y.dtype), _stream()), "moe_combine")
+                                    plan.top, dtype_code(out_dtype), dtype_code(y.dtype),
+                                    _ptr(plan.chosen) if plan.identity else None, plan.experts - plan.identity,
+                                    _ptr(h) if plan.identity else None, h.stride(0) if plan.identity else 0,
+                                    _ptr(plan.shared_gate) if shared_out is not None else None, _stream()), "moe_combine")
     return out
 
 
@@ -933,7 +999,7 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optional[t
         summed = out
         out = torch.empty(summed.shape, dtype=out_dtype, device=a.device)
         _check(library().vx_add_bias(_ptr(summed), _ptr(bias), _ptr(out), summed.shape[0], summed.shape[1],
-                                     dtype_code(out_dtype), _stream()), "add_bias")
+                                     dtype_code(out_dtype), 1.0, _stream()), "add_bias")
     return out
 
 

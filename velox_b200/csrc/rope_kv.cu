@@ -3,14 +3,15 @@
 // projection output.
 //
 // qkv is [tokens, row_stride] with, in each row, H query heads, then Hk key
-// heads, then Hk value heads, each of D elements.  One warp handles one head of
-// one token:
+// heads, each of D elements, then Hk value heads of Dv elements (Dv = D unless the
+// caller says otherwise; a row may go on with columns that are not touched here).
+// One warp handles one head of one token:
 //   q, k:  x = x * rsqrt(mean(x^2) + eps) * w[d]          (if a weight is given)
 //          pairs (i, i + rot/2), i < rot/2, rotated by angle = pos * inv_freq[i]
 //          (half-split convention; angle, sine and cosine in float32, computed
 //          here rather than read from a table rounded to the element type)
 //   q is written back in place; k goes to k_pool, v (untouched) to v_pool at
-//   slot_mapping[token] = page * S + offset, pools laid out [page, Hk, S, D].
+//   slot_mapping[token] = page * S + offset, pools laid out [page, Hk, S, D] and [page, Hk, S, Dv].
 // A token whose slot is negative writes nothing.  Without a slot mapping (a layer
 // that reads another layer's cache, or a caller that encodes positions itself)
 // nothing is written to the pools and the keys are normed and rotated in place.
@@ -26,7 +27,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
                                        const float* __restrict__ inv_freq, int rot_dim,
                                        const int* __restrict__ positions,
                                        const int* __restrict__ slot_mapping, T* __restrict__ k_pool,
-                                       T* __restrict__ v_pool, int H, int Hk, int D, int S) {
+                                       T* __restrict__ v_pool, int H, int Hk, int D, int S, int Dv) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float smem[];
@@ -41,8 +42,9 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
     if (head >= H + Hk) {  // value head: copy into the cache
         if (slot < 0) return;
         const int hk = head - H - Hk;
-        T* dst = v_pool + (((size_t)(slot / S) * Hk + hk) * S + (slot % S)) * D;
-        for (int d = lane; d < D; d += 32) dst[d] = src[d];
+        const T* vsrc = qkv + (size_t)t * row_stride + (size_t)(H + Hk) * D + (size_t)hk * Dv;
+        T* dst = v_pool + (((size_t)(slot / S) * Hk + hk) * S + (slot % S)) * Dv;
+        for (int d = lane; d < Dv; d += 32) dst[d] = vsrc[d];
         return;
     }
     const bool is_q = head < H;
@@ -220,13 +222,14 @@ extern "C" int vx_qk_norm_rope_kv(void* qkv, int row_stride, const float* q_weig
                                   const float* k_weight, float eps, const float* inv_freq,
                                   int rot_dim, const int* positions, const int* slot_mapping,
                                   void* k_pool, void* v_pool, int tokens, int H, int Hk, int D, int S,
-                                  int dtype, cudaStream_t stream) {
+                                  int dtype, int Dv, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
-    if (H <= 0 || Hk <= 0 || D <= 0 || S <= 0 || D > ROPE_MAX_D) return VX_ERR_SHAPE;
+    if (Dv <= 0) Dv = D;
+    if (H <= 0 || Hk <= 0 || D <= 0 || S <= 0 || D > ROPE_MAX_D || Dv > ROPE_MAX_D) return VX_ERR_SHAPE;
     if (rot_dim < 0 || rot_dim > D || (rot_dim & 1)) return VX_ERR_SHAPE;
-    if (row_stride < (H + 2 * Hk) * D) return VX_ERR_SHAPE;
+    if (row_stride < (H + Hk) * D + Hk * Dv) return VX_ERR_SHAPE;
     if (slot_mapping && (!k_pool || !v_pool)) return VX_ERR_SHAPE;
-    if (dtype == VX_BF16 && D == 128 && (rot_dim == D || !inv_freq) && !(row_stride & 3) &&
+    if (dtype == VX_BF16 && D == 128 && Dv == D && (rot_dim == D || !inv_freq) && !(row_stride & 3) &&
         !((((uintptr_t)qkv) | ((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 7)) {
         if (tokens >= ROPE128_TOKEN_MIN) {
             VX_LAUNCH_K(VX_K_ROPE, qk_norm_rope_kv_128_row_kernel, tokens, ROPE128_WARPS * 32, 0, stream, (bf16*)qkv,
@@ -246,10 +249,10 @@ extern "C" int vx_qk_norm_rope_kv(void* qkv, int row_stride, const float* q_weig
     const size_t smem = (size_t)ROPE_WARPS * D * sizeof(float);
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_kernel<float>), grid, ROPE_WARPS * 32, smem, stream, (float*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
-            (float*)k_pool, (float*)v_pool, H, Hk, D, S);
+            (float*)k_pool, (float*)v_pool, H, Hk, D, S, Dv);
     else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_kernel<bf16>), grid, ROPE_WARPS * 32, smem, stream, (bf16*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
-            (bf16*)k_pool, (bf16*)v_pool, H, Hk, D, S);
+            (bf16*)k_pool, (bf16*)v_pool, H, Hk, D, S, Dv);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

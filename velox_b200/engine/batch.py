@@ -56,6 +56,9 @@ class StepContext:
     max_kv_single: int = 0   # most keys of any of those requests after the step
     n_portions: int = 0      # requests that bring more
     max_short: int = 0       # the longest of the short requests (1: every row of `single_rows` is its request's only one)
+    # (residual, its rounding to the engine's element type) as the embedding or the last block left it, for a
+    # block whose sublayers read the stream itself; valid for the next block only (the model's loop drops it)
+    rounded: Optional[tuple] = None
 
     @property
     def decode_only(self) -> bool:

@@ -88,6 +88,7 @@ class DecoderModel:
     def forward_hidden(self, ctx, cache):
         """Runs the step's tokens through every layer; returns (residual, delta),
         whose sum is the last layer's output [tokens, hidden]."""
+        ctx.rounded = None
         if self._embedding_keeps_state():
             residual = self.embedding.forward(ctx, cache.layer(len(self.order)))
         else:
@@ -95,6 +96,8 @@ class DecoderModel:
         delta = None
         for place, i in enumerate(self.order):
             residual, delta = self.blocks[i].forward(residual, delta, ctx, cache.layer(place))
+            if not getattr(self.blocks[i], "leaves_rounded", False):
+                ctx.rounded = None   # (a rounded copy of the stream is good for the block right after its maker)
         return residual, delta
 
     def logits(self, residual, delta, rows: torch.Tensor) -> torch.Tensor:

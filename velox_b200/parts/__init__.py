@@ -1,7 +1,7 @@
 from .attention import PagedAttention
 from .base import (Block, CacheParts, Embedding, FeedForward, FixedState, Mixer, Norm, PagedKV, Part, Position, Runtime,
                    TensorSpec)
-from .block import PreNormBlock, SandwichNormBlock
+from .block import PostNormBlock, PreNormBlock, SandwichNormBlock
 from .embedding import OutputHead, PairHashEmbedding, TokenEmbedding
 from .linear import Linear, matmul
 from .linear_attention import DecayedLinearAttention
@@ -25,6 +25,7 @@ register_part("position", "rotary", RotaryPosition)
 register_part("position", "none", NoPosition)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)
+register_part("block", "post_norm", PostNormBlock)
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "pair_hash_embedding", PairHashEmbedding)
 register_part("head", "linear_head", OutputHead)

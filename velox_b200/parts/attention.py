@@ -20,8 +20,16 @@ to every later query, at their true distances), and `distance_bias_exponent` b >
 (head h's scores lose 2^(-b (h+1) / heads) * (query position - key position) before
 the softmax; 0: no bias).  With any of them the step's keys and values are written by
 the plain store kernel and the attention runs in the kernels that know them
-(`csrc/attention_biased.cu` for bfloat16, the general kernel otherwise); the q/k norm
-and the rotation need v_head_dim == head_dim.  `names` renames the four matrices.
+(`csrc/attention_biased.cu` for bfloat16, the general kernel otherwise).  `names` renames the four matrices
+and `norm_names` the two q/k norm weights.
+
+Two more, for designs that let a head attend to nothing and gate what it found:
+`sink` (a learned float32 per query head, tensor `sink_name`): the softmax's denominator also holds
+exp(sink_h), an entry without key or value that is not scaled, so a row's weights sum to less than one;
+`output_gate` (a matrix [heads, hidden], tensor `gate_name`): head h's output is multiplied by
+sigmoid(W_g x)_h before the output projection; W_g reads the mixer's input and rides as further rows of the
+fused projection matrix ([Wq; Wk; Wv; Wg], zero rows up to a multiple of 8), and the attention kernels apply
+the gate as they write a head's output.
 """
 from __future__ import annotations
 
@@ -58,12 +66,18 @@ class PagedAttention(Mixer):
                  bias: bool = False, qk_norm: bool = True, eps: float = 1e-6, window: int = 0,
                  position: Optional[PartSpec] = None, scale: Optional[float] = None, v_head_dim: int = 0,
                  keep_first: int = 0, distance_bias_exponent: float = 0.0,
-                 names: Sequence[str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight")):
+                 names: Sequence[str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight"),
+                 norm_names: Sequence[str] = ("q_norm.weight", "k_norm.weight"), sink: bool = False,
+                 output_gate: bool = False, sink_name: str = "sink", gate_name: str = "g"):
         super().__init__(prefix)
         self.names = dict(zip(("q_proj", "k_proj", "v_proj", "o_proj"), names))
+        self.norm_names = (prefix + norm_names[0], prefix + norm_names[1])
+        self.sink, self.output_gate = bool(sink), bool(output_gate)
+        self.sink_name, self.gate_name = prefix + sink_name, prefix + gate_name
+        self.sinks = None
         if num_heads % num_kv_heads:
             raise ValueError("num_heads %d is not a multiple of num_kv_heads %d" % (num_heads, num_kv_heads))
-        plain = position is None and not qk_norm   # (no rotation, no norm: the general kernel takes odd sizes too)
+        plain = position is None   # (no rotation: the norm and the general attention kernel take odd sizes too)
         if not (ops.attention_head_dim_supported(int(head_dim)) or (plain and 0 < int(head_dim) <= ops.ATTENTION_MAX_HEAD_DIM)):
             raise ValueError("%shead_dim %d: the attention kernels take even head sizes up to %d"
                              % (prefix, head_dim, ops.ATTENTION_MAX_HEAD_DIM))
@@ -71,8 +85,6 @@ class PagedAttention(Mixer):
         self.keep_first, self.bias_exponent = int(keep_first), float(distance_bias_exponent)
         if self.keep_first < 0 or self.bias_exponent < 0:
             raise ValueError("%skeep_first and distance_bias_exponent must not be negative" % prefix)
-        if self.v_head_dim != int(head_dim) and (qk_norm or position is not None or bias):
-            raise ValueError("%svalues of another size than keys go with plain projections (no q/k norm, rotation, bias)" % prefix)
         if not 0 < self.v_head_dim <= ops.ATTENTION_MAX_HEAD_DIM:
             raise ValueError("%sv_head_dim %d: the attention kernels take sizes up to %d"
                              % (prefix, self.v_head_dim, ops.ATTENTION_MAX_HEAD_DIM))
@@ -96,7 +108,15 @@ class PagedAttention(Mixer):
     @property
     def extended(self) -> bool:
         """True if the layer uses what only the kernels for biased, unequal or kept-first attention know."""
-        return self.v_head_dim != self.head_dim or self.keep_first > 0 or self.bias_exponent > 0
+        return (self.v_head_dim != self.head_dim or self.keep_first > 0 or self.bias_exponent > 0 or self.sink
+                or self.output_gate)
+
+    @property
+    def gate_col(self) -> int:
+        """The column of head 0's gate in a row of the fused projection, or -1."""
+        if not self.output_gate:
+            return -1
+        return (self.num_heads + self.num_kv_heads) * self.head_dim + self.num_kv_heads * self.v_head_dim
 
 
     def tensor_specs(self) -> List[TensorSpec]:
@@ -109,8 +129,12 @@ class PagedAttention(Mixer):
         if self.bias:
             specs.append(TensorSpec(p + "o_proj.bias", (self.hidden_size,), "bias"))
         if self.qk_norm:
-            specs.append(TensorSpec(p + "q_norm.weight", (self.head_dim,), "norm"))
-            specs.append(TensorSpec(p + "k_norm.weight", (self.head_dim,), "norm"))
+            specs.append(TensorSpec(self.norm_names[0], (self.head_dim,), "norm"))
+            specs.append(TensorSpec(self.norm_names[1], (self.head_dim,), "norm"))
+        if self.sink:
+            specs.append(TensorSpec(self.sink_name, (self.num_heads,), "bias"))
+        if self.output_gate:
+            specs.append(TensorSpec(self.gate_name, (self.num_heads, self.hidden_size), "matrix"))
         if self.position is not None:
             specs.extend(self.position.tensor_specs())
         return specs
@@ -121,12 +145,24 @@ class PagedAttention(Mixer):
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(tensors, runtime)
         p = self.prefix
-        w = torch.cat([tensors[self._w(n)] for n in ("q_proj", "k_proj", "v_proj")], dim=0).contiguous()
-        b = torch.cat([tensors[p + n + ".bias"] for n in ("q_proj", "k_proj", "v_proj")]).contiguous() if self.bias else None
+        mats = [tensors[self._w(n)] for n in ("q_proj", "k_proj", "v_proj")]
+        biases = [tensors[p + n + ".bias"] for n in ("q_proj", "k_proj", "v_proj")] if self.bias else None
+        if self.output_gate:
+            # the gates' rows, then zero rows up to a multiple of 8 (rows of the projection stay 16-byte aligned)
+            g = tensors[self.gate_name]
+            rows = sum(m.shape[0] for m in mats) + g.shape[0]
+            mats += [g, torch.zeros(((-rows) % 8, self.hidden_size), dtype=g.dtype, device=g.device)]
+            if biases is not None:
+                biases.append(torch.zeros(mats[-2].shape[0] + mats[-1].shape[0], dtype=biases[0].dtype, device=g.device))
+        w = torch.cat(mats, dim=0).contiguous()
+        b = torch.cat(biases).contiguous() if biases is not None else None
+        del mats
         self.qkv = Linear(w, b)
+        if self.sink:
+            self.sinks = tensors[self.sink_name].to(torch.float32).contiguous()
         self.out = Linear(tensors[self._w("o_proj")], tensors[p + "o_proj.bias"] if self.bias else None)
         if self.qk_norm:
-            self.q_norm_weight, self.k_norm_weight = tensors[p + "q_norm.weight"], tensors[p + "k_norm.weight"]
+            self.q_norm_weight, self.k_norm_weight = tensors[self.norm_names[0]], tensors[self.norm_names[1]]
         if self.position is not None:
             self.position.bind(tensors, runtime)
 
@@ -153,12 +189,12 @@ class PagedAttention(Mixer):
         if self.position is None or rotary is not None:
             inv_freq, rot = rotary if rotary is not None else (None, 0)
             ops.qk_norm_rope_kv(qkv, qw, kw, self.eps, inv_freq, rot, ctx.positions, slots,
-                                cache.k_pool, cache.v_pool, H, Hk, D)
+                                cache.k_pool, cache.v_pool, H, Hk, D, self.v_head_dim)
         else:
             # An encoding the fused kernel does not know: norm in place, let the
             # part encode q and k in place, then write the cache.
             t = qkv.shape[0]
-            ops.qk_norm_rope_kv(qkv, qw, kw, self.eps, None, 0, ctx.positions, None, None, None, H, Hk, D)
+            ops.qk_norm_rope_kv(qkv, qw, kw, self.eps, None, 0, ctx.positions, None, None, None, H, Hk, D, self.v_head_dim)
             q, k = qkv[:, : H * D].view(t, H, D), qkv[:, H * D : (H + Hk) * D].view(t, Hk, D)
             q2, k2 = self.position.apply(q, k, ctx.positions)
             if q2 is not q:
@@ -166,27 +202,28 @@ class PagedAttention(Mixer):
             if k2 is not k:
                 k.copy_(k2)
             ops.qk_norm_rope_kv(qkv, None, None, self.eps, None, 0, ctx.positions, slots,
-                                cache.k_pool, cache.v_pool, H, Hk, D)
+                                cache.k_pool, cache.v_pool, H, Hk, D, self.v_head_dim)
         attn = self._attend_extended(qkv, ctx, cache, group) if self.extended else self._attend(qkv, ctx, cache, group)
         return self.out(attn)
 
     def _attend_extended(self, qkv, ctx, cache, group) -> torch.Tensor:
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
+        more = dict(sinks=self.sinks, gate_col=self.gate_col)
         if ops.biased_attention_supported(qkv.dtype, D, self.v_head_dim, cache.k_pool.shape[2]):
             # a step of single tokens: every row with its own position, its keys dealt to the warps of a block
             if ctx.decode_only:
                 return ops.biased_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                                    ctx.seq_of_token, ctx.positions, self.scale, self.window,
                                                    self.keep_first, self.bias_exponent, H, Hk, D, self.v_head_dim,
-                                                   qkv.shape[0], max_kv=ctx.max_kv)
+                                                   qkv.shape[0], max_kv=ctx.max_kv, **more)
             return ops.biased_prefill_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                                 ctx.cu_seqlens, ctx.kv_offsets, self.scale, self.window, self.keep_first,
                                                 self.bias_exponent, H, Hk, D, self.v_head_dim, ctx.n_seqs, ctx.max_new,
-                                                qkv.shape[0])
+                                                qkv.shape[0], **more)
         return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                            ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                            qkv.shape[0], v_head_dim=self.v_head_dim, keep_first=self.keep_first,
-                                           bias_exponent=self.bias_exponent)
+                                           bias_exponent=self.bias_exponent, **more)
 
     def _attend(self, qkv, ctx, cache, group) -> torch.Tensor:
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim

@@ -4,7 +4,9 @@ x[t] = embed_tokens.weight[id[t]] (src/paged/qwen3.rs:958, 998); logits =
 rows W^T with W the head's own matrix, or the embedding table when the two are
 tied (src/paged/qwen3.rs:966-976).  The embedding feeds the float32 residual
 stream; logits are always float32 (the reference leaves them in the model's
-element type, src/paged/qwen3.rs:1015).
+element type, src/paged/qwen3.rs:1015).  Two multipliers for designs that have them:
+`TokenEmbedding(scale=)` on the rows that enter the stream, `OutputHead(logit_scale=)`
+on the float32 logits.
 """
 from __future__ import annotations
 
@@ -20,20 +22,30 @@ from .linear import matmul
 class TokenEmbedding(Embedding):
     cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int):
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, scale: float = 1.0, weight_name: str = "weight",
+                 leaves_rounded: bool = False):
         super().__init__(prefix)
-        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.vocab_size, self.hidden_size, self.scale = int(vocab_size), int(hidden_size), float(scale)
+        self.weight_name = prefix + weight_name
+        # for a first block whose sublayers read the stream itself: the rows also go to `ctx.rounded`
+        # in the engine's element type, from the same kernel
+        self.leaves_rounded = bool(leaves_rounded)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.prefix + "weight", (self.vocab_size, self.hidden_size), "table")]
+        return [TensorSpec(self.weight_name, (self.vocab_size, self.hidden_size), "table")]
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(tensors, runtime)
-        self.weight = tensors[self.prefix + "weight"]
+        self.weight = tensors[self.weight_name]
 
     def forward(self, ctx) -> torch.Tensor:
-        return ops.embedding(ctx.token_ids, self.weight)
+        if not self.leaves_rounded:
+            return ops.embedding(ctx.token_ids, self.weight, scale=self.scale)
+        rounded = torch.empty((ctx.token_ids.numel(), self.hidden_size), dtype=self.weight.dtype, device=self.weight.device)
+        x = ops.embedding(ctx.token_ids, self.weight, scale=self.scale, rounded=rounded)
+        ctx.rounded = (x, rounded)
+        return x
 
 
 class PairHashEmbedding(Embedding):
@@ -74,9 +86,11 @@ class PairHashEmbedding(Embedding):
 class OutputHead(Part):
     cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied: bool = False, weight_name: str = "weight"):
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied: bool = False, weight_name: str = "weight",
+                 logit_scale: float = 1.0):
         super().__init__(prefix)
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
+        self.logit_scale = float(logit_scale)
         self.weight_name = prefix + weight_name
         self.weight: Optional[torch.Tensor] = None
 
@@ -98,4 +112,5 @@ class OutputHead(Part):
         self.weight = table
 
     def forward(self, rows: torch.Tensor) -> torch.Tensor:
-        return matmul(rows, self.weight, None, torch.float32)
+        logits = matmul(rows, self.weight, None, torch.float32)
+        return logits if self.logit_scale == 1.0 else ops.scale_rows(logits, self.logit_scale)
