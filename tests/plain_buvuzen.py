@@ -175,14 +175,19 @@ def routed_ff(h, w, p, c, store=keep, margins_out=None):
 
 
 def layer_sources(cfg):
-    """Per layer the layer whose tensors it uses (itself, or its `weights_of`)."""
-    return [int(layer["weights_of"]) if layer.get("weights_of") is not None else i for i, layer in enumerate(cfg["layers"])]
+    """Per layer the layer whose tensors it uses: itself, or the one its `weights_of` leads to."""
+    out = []
+    for i in range(len(cfg["layers"])):
+        while cfg["layers"][i].get("weights_of") is not None:
+            i = int(cfg["layers"][i]["weights_of"])
+        out.append(i)
+    return out
 
 
 def forward(cfg, w, ids, store=keep, layers_out=None, margins_out=None):
     """Logits [T, vocab] of the whole sequence `ids`."""
     eps = float(cfg["norm"]["eps"])
-    x = scaled_embedding(ids, w["embed"], float(cfg["embedding"]["scale"]))
+    x = scaled_embedding(ids, w["embed"], float((cfg.get("embedding") or {}).get("scale", 1.0)))
     for i, src in enumerate(layer_sources(cfg)):
         layer, p = cfg["layers"][src], "l%d." % src
         x = x + one_plus_norm(attention_mixer(x, w, p + "mix.", layer["mixer"], eps, store), w[p + "norm1"], eps)
@@ -191,7 +196,7 @@ def forward(cfg, w, ids, store=keep, layers_out=None, margins_out=None):
         if layers_out is not None:
             layers_out.append(x.copy())
     h = store(one_plus_norm(x, w["final.norm"], eps))
-    return (h @ w["head"].T) * float(cfg["logit_scale"])
+    return (h @ w["head"].T) * float(cfg.get("logit_scale", 1.0))
 
 
 def greedy_generate(cfg, w, prompt, new_tokens):
