@@ -225,89 +225,69 @@ def qwen_raw_like(sz):
                 intermediate_size=DOBEPEL_TOP * sz["expert_ff"] + sz["shared_ff"], tie_word_embeddings=False)
 
 
-def dobepel_workload(args, pk):
-    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at 2,048 cached tokens) of Dobepel
-    and of Qwen3 at equal size, through the step function, timed with CUDA events; then the design's own kernels
-    beside the like kernels of Qwen3 at the 2k size, each as a fraction of its roofline."""
+def timed(fn, steps):
+    """Milliseconds a call of `fn`, by CUDA events around `steps` calls."""
+    import torch
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def model_points(cfg, vocab, T, B, CTX, K, W, gen):
+    """Prefill (one prompt of T tokens in one step) and decode (batch B at CTX cached tokens) of a model with
+    random weights through the step function."""
     import torch
     from velox_b200 import Engine, EngineConfig
-    from velox_b200.config import DobepelConfig, Qwen3Config
     from velox_b200.csrc import ops
     from velox_b200.engine import StepEntry
+    eng = Engine(model_config=cfg, random_seed=SEED, config=EngineConfig(
+        dtype="bfloat16", page_size=PAGE, num_pages=(B + 1) * ((CTX + 64) // PAGE + 1), max_running_requests=B + 1,
+        max_batch_tokens=T, max_model_len=CTX + 64))
+    toks = torch.randint(0, vocab, (B + 1, CTX), generator=gen).tolist()
 
-    T, B, CTX = 2048, 8, 2048
-    K, W = max(1, min(args.steps, 32)), max(3, args.warmup)
-    gen = torch.Generator().manual_seed(SEED)
+    def prefill():
+        eng.cache.add_request("p")
+        eng.run_step([StepEntry("p", toks[B][:T], [T - 1])])
+        eng.cache.release("p")
+    for _ in range(3):
+        prefill()
+    pms = timed(prefill, 5)
+    for i in range(B):
+        eng.cache.add_request(i)
+        eng.run_step([StepEntry(i, toks[i][:CTX - K - W - 2], [])])
+    entries = [StepEntry(i, [toks[i][-1]], [0]) for i in range(B)]
+    zeros, ones = [0.0] * B, [1.0] * B
 
-    def timed(fn, steps):
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(steps):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / steps
-
-    def model_points(cfg, vocab):
-        eng = Engine(model_config=cfg, random_seed=SEED, config=EngineConfig(
-            dtype="bfloat16", page_size=PAGE, num_pages=(B + 1) * ((CTX + 64) // PAGE + 1), max_running_requests=B + 1,
-            max_batch_tokens=T, max_model_len=CTX + 64))
-        toks = torch.randint(0, vocab, (B + 1, CTX), generator=gen).tolist()
-
-        def prefill():
-            eng.cache.add_request("p")
-            eng.run_step([StepEntry("p", toks[B][:T], [T - 1])])
-            eng.cache.release("p")
-        for _ in range(3):
-            prefill()
-        pms = timed(prefill, 5)
-        for i in range(B):
-            eng.cache.add_request(i)
-            eng.run_step([StepEntry(i, toks[i][:CTX - K - W - 2], [])])
-        entries = [StepEntry(i, [toks[i][-1]], [0]) for i in range(B)]
-        zeros, ones = [0.0] * B, [1.0] * B
-
-        def step():
-            eng.runner.step_and_sample(entries, zeros, ones, zeros)
-        for _ in range(W):
-            step()
-        n0 = ops.launch_count()
-        dms = timed(step, K)
-        launches = (ops.launch_count() - n0) // K
-        ops.check_device_errors()
-        del eng
-        torch.cuda.empty_cache()
-        return {"prefill_ms": round(pms, 3), "prefill_tok_s": round(T * 1000.0 / pms, 1), "decode_ms_per_step": round(dms, 4),
-                "decode_tok_s": round(B * 1000.0 / dms, 1), "launches_per_decode_step": int(launches)}
-
-    sizes = {}
-    for name, sz in DOBEPEL_SIZES.items():
-        sizes[name] = {"dobepel": model_points(DobepelConfig.from_dict(dobepel_raw(sz)), DOBEPEL_VOCAB),
-                       "qwen3": model_points(Qwen3Config.from_dict(qwen_raw_like(sz)), DOBEPEL_VOCAB), "shape": sz}
-    out = {"metric": "Dobepel beside Qwen3 at equal size: prefill of %d tokens, decode at batch %d with %d cached tokens, bf16"
-                     % (T, B, CTX), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "sizes": sizes,
-           "value": sizes["2k"]["dobepel"]["decode_tok_s"], "higher_is_better": True,
-           "kernels": dobepel_kernels(pk, DOBEPEL_SIZES["2k"], timed), "peaks": pk,
-           "data": "synthetic: random weights N(0,0.02) seed 2, uniform random token ids; inputs of the kernel rows rotate "
-                   "through buffers larger than L2 where they are bound by memory"}
-    return out
+    def step():
+        eng.runner.step_and_sample(entries, zeros, ones, zeros)
+    for _ in range(W):
+        step()
+    n0 = ops.launch_count()
+    dms = timed(step, K)
+    launches = (ops.launch_count() - n0) // K
+    ops.check_device_errors()
+    del eng
+    torch.cuda.empty_cache()
+    return {"prefill_ms": round(pms, 3), "prefill_tok_s": round(T * 1000.0 / pms, 1), "decode_ms_per_step": round(dms, 4),
+            "decode_tok_s": round(B * 1000.0 / dms, 1), "launches_per_decode_step": int(launches)}
 
 
-def dobepel_kernels(pk, sz, timed):
-    """Microseconds and fractions of the roofline of Dobepel's kernels and of Qwen3's like kernels at one size."""
+def kernel_rows(pk):
+    """(rows, row, us): a table of kernel timings; `row(name, microseconds, flops, bytes)` adds a line with its fraction
+    of the roofline; `us(fn, n)` measures a call."""
     import torch
-    from velox_b200.csrc import ops
-    dev, bf = "cuda:0", torch.bfloat16
-    E, H, G, HL, D = sz["width"], sz["heads"], sz["kv_heads"], sz["lin_heads"], 128
-    T, B, CTX, S, win, keep = 2048, 8, 2048, PAGE, DOBEPEL_WINDOW, DOBEPEL_KEEP
     hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
     rows = {}
 
-    def row(name, us, flops=0.0, nbytes=0.0):
-        t = us * 1e-6
+    def row(name, us_, flops=0.0, nbytes=0.0):
+        t = us_ * 1e-6
         frac_c, frac_m = flops / t / tf, nbytes / t / hbm
-        rows[name] = {"us": round(us, 2), "bound": "tensor" if frac_c >= frac_m else "hbm",
+        rows[name] = {"us": round(us_, 2), "bound": "tensor" if frac_c >= frac_m else "hbm",
                       "frac": round(max(frac_c, frac_m), 4)}
 
     def us(fn, n=20):
@@ -323,6 +303,42 @@ def dobepel_kernels(pk, sz, timed):
         for _ in range(3):
             g.replay()
         return timed(g.replay, 5) * 1000.0 / n
+    return rows, row, us
+
+
+def dobepel_workload(args, pk):
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at 2,048 cached tokens) of Dobepel
+    and of Qwen3 at equal size, through the step function, timed with CUDA events; then the design's own kernels
+    beside the like kernels of Qwen3 at the 2k size, each as a fraction of its roofline."""
+    import torch
+    from velox_b200.config import DobepelConfig, Qwen3Config
+
+    T, B, CTX = 2048, 8, 2048
+    K, W = max(1, min(args.steps, 32)), max(3, args.warmup)
+    gen = torch.Generator().manual_seed(SEED)
+
+    sizes = {}
+    for name, sz in DOBEPEL_SIZES.items():
+        sizes[name] = {"dobepel": model_points(DobepelConfig.from_dict(dobepel_raw(sz)), DOBEPEL_VOCAB, T, B, CTX, K, W, gen),
+                       "qwen3": model_points(Qwen3Config.from_dict(qwen_raw_like(sz)), DOBEPEL_VOCAB, T, B, CTX, K, W, gen),
+                       "shape": sz}
+    out = {"metric": "Dobepel beside Qwen3 at equal size: prefill of %d tokens, decode at batch %d with %d cached tokens, bf16"
+                     % (T, B, CTX), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "sizes": sizes,
+           "value": sizes["2k"]["dobepel"]["decode_tok_s"], "higher_is_better": True,
+           "kernels": dobepel_kernels(pk, DOBEPEL_SIZES["2k"]), "peaks": pk,
+           "data": "synthetic: random weights N(0,0.02) seed 2, uniform random token ids; inputs of the kernel rows rotate "
+                   "through buffers larger than L2 where they are bound by memory"}
+    return out
+
+
+def dobepel_kernels(pk, sz):
+    """Microseconds and fractions of the roofline of Dobepel's kernels and of Qwen3's like kernels at one size."""
+    import torch
+    from velox_b200.csrc import ops
+    dev, bf = "cuda:0", torch.bfloat16
+    E, H, G, HL, D = sz["width"], sz["heads"], sz["kv_heads"], sz["lin_heads"], 128
+    T, B, CTX, S, win, keep = 2048, 8, 2048, PAGE, DOBEPEL_WINDOW, DOBEPEL_KEEP
+    rows, row, us = kernel_rows(pk)
     ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
     pages = B * (CTX // S)
     kp = torch.randn((pages, G, S, D), device=dev).to(bf)
@@ -411,6 +427,143 @@ def dobepel_kernels(pk, sz, timed):
     return rows
 
 
+# ---- Buvuzen beside Dobepel and Qwen3 at equal size (`--workload buvuzen`) ------------------------------
+# The same layer sizes as above: heads of 128 with values of 128, window 1,024, 8 experts and 2 identity experts in
+# 5 groups of which 3 are kept, 2 chosen, a gated shared expert.  Dobepel is the closest existing model (attention
+# without rotation under a window through the same kernels, routed experts with a shared one; it has a linear-attention
+# member more), Qwen3 the dense one with the same q/k norm.
+BUVUZEN_IDENTITY, BUVUZEN_GROUPS, BUVUZEN_KEEP = 2, 5, 3
+
+
+def buvuzen_raw(sz):
+    mixer = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+             "mask": {"size": DOBEPEL_WINDOW}}
+    mlp = {"kind": "moe", "expert": {"ff": sz["expert_ff"]},
+           "router": {"experts": DOBEPEL_EXPERTS, "identity": BUVUZEN_IDENTITY, "top": DOBEPEL_TOP, "scale": 2.0,
+                      "groups": {"count": BUVUZEN_GROUPS, "keep": BUVUZEN_KEEP}}, "shared": {"ff": sz["shared_ff"]}}
+    layer = {"type": "attention", "mixer": mixer, "mlp": mlp}
+    return {"architecture": "Buvuzen", "vocab": DOBEPEL_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 2.0}, "logit_scale": 0.5, "layers": [json.loads(json.dumps(layer)) for _ in range(sz["layers"])]}
+
+
+def buvuzen_workload(args, pk):
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at 2,048 cached tokens) of Buvuzen, of
+    Dobepel and of Qwen3 at equal size, through the step function, timed with CUDA events; then the kernels that the
+    design added or changed beside the like kernels of the other two at the 2k size, each as a fraction of its roofline."""
+    import torch
+    from velox_b200.config import BuvuzenConfig, DobepelConfig, Qwen3Config
+
+    T, B, CTX = 2048, 8, 2048
+    K, W = max(1, min(args.steps, 32)), max(3, args.warmup)
+    gen = torch.Generator().manual_seed(SEED)
+    sizes = {}
+    for name, sz in DOBEPEL_SIZES.items():
+        sizes[name] = {"buvuzen": model_points(BuvuzenConfig.from_dict(buvuzen_raw(sz)), DOBEPEL_VOCAB, T, B, CTX, K, W, gen),
+                       "dobepel": model_points(DobepelConfig.from_dict(dobepel_raw(sz)), DOBEPEL_VOCAB, T, B, CTX, K, W, gen),
+                       "qwen3": model_points(Qwen3Config.from_dict(qwen_raw_like(sz)), DOBEPEL_VOCAB, T, B, CTX, K, W, gen),
+                       "shape": sz}
+    return {"metric": "Buvuzen beside Dobepel and Qwen3 at equal size: prefill of %d tokens, decode at batch %d with %d cached "
+                      "tokens, bf16" % (T, B, CTX), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "sizes": sizes,
+            "value": sizes["2k"]["buvuzen"]["decode_tok_s"], "higher_is_better": True,
+            "kernels": buvuzen_kernels(pk, DOBEPEL_SIZES["2k"]), "peaks": pk,
+            "data": "synthetic: random weights N(0,0.02) seed 2, uniform random token ids; inputs of the kernel rows rotate "
+                    "through buffers larger than L2 where they are bound by memory"}
+
+
+def buvuzen_kernels(pk, sz):
+    """Microseconds and fractions of the roofline of the kernels Buvuzen added to or changed, beside the like kernels of
+    Dobepel and Qwen3 at one size.  (The grouped products of the experts and the dense products are the same kernels as
+    Dobepel's and Qwen3's: `--workload dobepel` has their rows.)"""
+    import torch
+    from velox_b200.csrc import ops
+    dev, bf = "cuda:0", torch.bfloat16
+    E, H, G, D = sz["width"], sz["heads"], sz["kv_heads"], 128
+    T, B, CTX, S, win, keep = 2048, 8, 2048, PAGE, DOBEPEL_WINDOW, DOBEPEL_KEEP
+    rows, row, us = kernel_rows(pk)
+    ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    pages = B * (CTX // S)
+    kp = torch.randn((pages, G, S, D), device=dev).to(bf)
+    vp = torch.randn((pages, G, S, D), device=dev).to(bf)
+    bt = torch.arange(pages, dtype=torch.int32, device=dev).view(B, CTX // S)
+    sinks = torch.randn(H, device=dev)
+    width = (H + 2 * G) * D + (H + 7) // 8 * 8     # q | k | v | gates (padded to 8)
+    gate_col = (H + 2 * G) * D
+    # -- attention over a prompt of T tokens (one request), window 1,024 --
+    q = torch.randn((T, width), device=dev).to(bf)
+    cu, off = ints([0, T]), ints([0])
+    fl = 2.0 * sum(min(i + 1, win) for i in range(T)) * 2 * D * H
+    flk = 2.0 * sum(min(i + 1, win) + (min(keep, i + 1 - win) if i + 1 > win else 0) for i in range(T)) * 2 * D * H
+    row("prompt attention, window + sink + gate (mma.sync, P in two halves)", us(lambda: ops.biased_prefill_attention(
+        q, width, kp, vp, bt, cu, off, D ** -0.5, win, 0, 0.0, H, G, D, D, 1, T, T, sinks=sinks, gate_col=gate_col)), fl)
+    row("prompt attention, Dobepel (biased window, kept first tokens)", us(lambda: ops.biased_prefill_attention(
+        q, width, kp, vp, bt, cu, off, D ** -0.5, win, keep, 8.0, H, G, D, D, 1, T, T)), flk)
+    row("prompt attention, Qwen3 (tcgen05)", us(lambda: ops.paged_prefill_attention_tc(
+        q, width, kp, vp, bt, cu, off, D ** -0.5, win, H, G, D, 1, T, T)), fl)
+    # -- attention of B single tokens at CTX cached tokens --
+    qd = torch.randn((B, width), device=dev).to(bf)
+    seqs, pos = ints(list(range(B))), ints([CTX - 1] * B)
+    row("decode attention, window + sink + gate", us(lambda: ops.biased_decode_attention(
+        qd, width, kp, vp, bt, seqs, pos, D ** -0.5, win, 0, 0.0, H, G, D, D, B, max_kv=CTX, sinks=sinks, gate_col=gate_col), 50),
+        0.0, B * G * win * 2 * D * 2.0)
+    row("decode attention, Dobepel (biased window)", us(lambda: ops.biased_decode_attention(
+        qd, width, kp, vp, bt, seqs, pos, D ** -0.5, win, keep, 8.0, H, G, D, D, B, max_kv=CTX), 50),
+        0.0, B * G * (win + keep) * 2 * D * 2.0)
+    row("decode attention, Qwen3", us(lambda: ops.paged_decode_attention(
+        qd, width, kp, vp, bt, seqs, pos, D ** -0.5, win, H, G, D, B, CTX), 50), 0.0, B * G * win * 2 * D * 2.0)
+    # -- q/k norm and the write of keys and values into the pages (no rotation here; Qwen3 rotates) --
+    slots = torch.randperm(pages * S, device=dev)[:T].to(torch.int32)
+    wn = torch.ones(D, device=dev)
+    positions = ints(list(range(T)))
+    inv_freq = (1e6 ** (-torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D)).contiguous()
+    nb = T * (H + 2 * G) * D * 2 * 2.0
+    row("q/k norm + cache write, %d tokens" % T, us(lambda: ops.qk_norm_rope_kv(
+        q, wn, wn, 1e-6, None, 0, positions, slots, kp, vp, H, G, D, D)), 0.0, nb)
+    row("q/k norm + rotation + cache write, Qwen3, %d tokens" % T, us(lambda: ops.qk_norm_rope_kv(
+        q, wn, wn, 1e-6, inv_freq, D, positions, slots, kp, vp, H, G, D)), 0.0, nb)
+    # -- router and combination --
+    NE, ident, top, F = DOBEPEL_EXPERTS, BUVUZEN_IDENTITY, DOBEPEL_TOP, sz["expert_ff"]
+    R = NE + ident
+    h = torch.randn((T, E), device=dev).to(bf)
+    wr = torch.randn((R + 1, E), device=dev) * 0.1
+    corr = torch.randn(R, device=dev) * 0.05
+    route_b = lambda x, rows_: ops.moe_route(x, wr, None, R, top, rows_, scores="softmax_all", correction=corr,
+                                             groups=BUVUZEN_GROUPS, keep_groups=BUVUZEN_KEEP, route_scale=2.0, identity=ident,
+                                             shared_gate=True)
+    wr_d = wr[:NE].contiguous()
+    row("router and plan, %d tokens (softmax over all, groups, shared gate)" % T, us(lambda: route_b(h, ops.MOE_TCGEN05_TILE_ROWS)),
+        0.0, T * E * 2.0)
+    row("router and plan, Dobepel, %d tokens" % T, us(lambda: ops.moe_route(h, wr_d, None, NE, top, ops.MOE_TCGEN05_TILE_ROWS)),
+        0.0, T * E * 2.0)
+    plan, plan_d = route_b(h, ops.MOE_TCGEN05_TILE_ROWS), ops.moe_route(h, wr_d, None, NE, top, ops.MOE_TCGEN05_TILE_ROWS)
+    y = torch.randn((T * top, E), device=dev).to(bf)
+    shared = torch.randn((T, E), device=dev).to(bf)
+    nbc = T * E * 2.0 * (top + 2)
+    row("combination with identity experts and a gated shared expert, %d tokens" % T,
+        us(lambda: ops.moe_combine(y, plan, shared, bf, h=h)), 0.0, nbc + T * E * 2.0)
+    row("combination, Dobepel, %d tokens" % T, us(lambda: ops.moe_combine(y, plan_d, shared, bf)), 0.0, nbc)
+    hd = torch.randn((B, E), device=dev).to(bf)
+    row("router and plan, %d tokens (decode)" % B, us(lambda: route_b(hd, ops.MOE_SMALL_TILE_ROWS), 50), 0.0, (R + 1) * E * 4.0)
+    row("router and plan, Dobepel, %d tokens (decode)" % B,
+        us(lambda: ops.moe_route(hd, wr_d, None, NE, top, ops.MOE_SMALL_TILE_ROWS), 50), 0.0, NE * E * 4.0)
+    # -- norms and residual --
+    big = 16384   # rows: float32 residual + a branch, far larger than L2
+    res = torch.randn((big, E), device=dev)
+    y0, y1 = torch.randn((big, E), device=dev).to(bf), torch.randn((big, E), device=dev).to(bf)
+    w = torch.ones(E, device=dev)
+    row("norm of a sublayer's output + residual + rounded stream, %d rows" % big,
+        us(lambda: ops.merge_norm_add_norm(res, y0, w, 1.0, 1e-6, rounded=True), 10), 0.0, big * E * (4 + 4 + 2 + 2.0))
+    row("Dobepel: two branch norms + sum + norm + residual + next norm, %d rows" % big,
+        us(lambda: ops.merge_norm_add_norm(res, y0, w, 0.5, 1e-6, w, 0.5, y1, w, 0.5, w_next=w), 10), 0.0, big * E * (4 + 4 + 2 + 2 + 2.0))
+    row("Qwen3 residual add + norm, %d rows" % big, us(lambda: ops.add_rmsnorm(res, y0, w, 1e-6, bf), 10), 0.0, big * E * (4 + 4 + 2 + 2.0))
+    tok = torch.randint(0, DOBEPEL_VOCAB, (big,), device=dev, dtype=torch.int32)
+    table = torch.randn((DOBEPEL_VOCAB, E), device=dev).to(bf)
+    rounded = torch.empty((big, E), device=dev, dtype=bf)
+    row("embedding times a number + rounded stream, %d rows" % big, us(lambda: ops.embedding(tok, table, scale=2.0, rounded=rounded), 10),
+        0.0, big * E * (2 + 4 + 2.0))
+    row("embedding, Qwen3, %d rows" % big, us(lambda: ops.embedding(tok, table), 10), 0.0, big * E * (2 + 4.0))
+    return rows
+
+
 def main() -> int:
     global CONTEXT, PROMPT
     ap = argparse.ArgumentParser()
@@ -420,11 +573,12 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (recorded in config)")
     ap.add_argument("--batch", type=int, default=BATCH)
-    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "dobepel"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "dobepel", "buvuzen"],
                     help="decode: the benchmark (steady decoding at a fixed batch). stream: continuous batching "
                          "under arrivals (64 requests, prompts of 128-4,096 tokens, 256 new tokens each, Poisson "
                          "arrivals); prints its own JSON line. dobepel: the Dobepel design beside Qwen3 at equal size "
-                         "(prefill, decode, and the design's kernels against their rooflines); its own JSON line")
+                         "(prefill, decode, and the design's kernels against their rooflines); its own JSON line. buvuzen: the same for "
+                         "the Buvuzen design beside Dobepel and Qwen3")
     ap.add_argument("--arrival-rate", type=float, default=16.0, help="stream: mean arrivals a second")
     ap.add_argument("--lazy-graphs", action="store_true",
                     help="stream: capture each decode graph when a step first needs it, inside the run")
@@ -455,9 +609,9 @@ def main() -> int:
     from velox_b200.csrc import ops
     from velox_b200.engine import StepEntry
 
-    if args.workload == "dobepel":
+    if args.workload in ("dobepel", "buvuzen"):
         with ClockSampler() as clocks:
-            res = dobepel_workload(args, peaks())
+            res = (dobepel_workload if args.workload == "dobepel" else buvuzen_workload)(args, peaks())
         res["clocks"] = clocks.summary()
         print(json.dumps(res))
         return 0
