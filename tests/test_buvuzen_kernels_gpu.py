@@ -143,10 +143,13 @@ KERNELS = [("general", torch.float32), ("general", torch.bfloat16), ("single", t
 
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
 @pytest.mark.parametrize("H,G,Dk,Dv,size", [(4, 2, 64, 32, 40), (8, 1, 64, 128, 100), (2, 2, 128, 64, 16), (4, 4, 64, 64, 300),
-                                            (6, 2, 128, 128, 33), (3, 3, 64, 64, 0), (4, 2, 24, 20, 9), (5, 1, 48, 56, 70)])
+                                            (6, 2, 128, 128, 33), (3, 3, 64, 64, 0), (4, 2, 24, 20, 9), (5, 1, 48, 56, 70),
+                                            (6, 3, 48, 48, 50), (4, 1, 32, 32, 21), (2, 2, 80, 80, 64), (4, 2, 96, 96, 17),
+                                            (3, 1, 112, 112, 130)])
 def test_sink_and_gate_attention_against_the_plain_function(kernel, dtype, H, G, Dk, Dv, size):
-    if kernel != "general" and (Dk not in (64, 128) or Dv not in (32, 64, 128)):
-        pytest.skip("the tensor-core kernels take keys of 64 and 128, values of 32, 64 and 128")
+    from velox_b200.csrc import ops
+    if kernel != "general" and not ops.biased_attention_supported(dtype, Dk, Dv, 16):
+        pytest.skip("sizes the tensor-core kernels do not take")
     rng = np.random.default_rng(H * (size + 1))
     T, S, scale = 200, 16, 0.11
     q, k, v = bf(rng.normal(size=(T, H, Dk))), bf(rng.normal(size=(T, G, Dk))), bf(rng.normal(size=(T, G, Dv)))
@@ -190,13 +193,14 @@ def test_a_sink_above_every_score_empties_the_row_and_one_far_below_changes_noth
             assert np.abs(g[0, 2] - 0.5 * v[0, 1]).max() <= TOL[dtype] * max(1.0, np.abs(v).max())
 
 
+@pytest.mark.parametrize("Dk,Dv", [(64, 32), (48, 48), (96, 96)])
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
-def test_one_key_that_stands_out_is_seen_exactly_as_long_as_the_window_says(kernel, dtype):
+def test_one_key_that_stands_out_is_seen_exactly_as_long_as_the_window_says(kernel, dtype, Dk, Dv):
     """One key is made to dominate (a large dot product with every query) and its value is marked.  A query sees the
     mark iff the key is inside its window: at the window's last position and not one further, far away under no window,
     at page borders, with the key in the request's first page, in a prompt's portion and for single tokens.  A closed
     gate hides it again."""
-    H, G, Dk, Dv, S, scale, T = 4, 2, 64, 32, 16, 0.25, 330
+    H, G, S, scale, T = 4, 2, 16, 0.25, 330
     rng = np.random.default_rng(4)
     sinks = np.asarray([0.0, 3.0, -2.0, 1.0])
     for size, spike in ((48, 2), (48, 100), (32, 15), (32, 16), (64, 0), (17, 191), (0, 1), (1, 200), (300, 17)):
@@ -227,7 +231,8 @@ def test_one_key_that_stands_out_is_seen_exactly_as_long_as_the_window_says(kern
                 assert abs(g[2, 0]) < 1e-9
 
 
-@pytest.mark.parametrize("H,G,Dk,Dv,size", [(8, 2, 128, 128, 1200), (4, 4, 64, 32, 600), (6, 2, 64, 64, 0)])
+@pytest.mark.parametrize("H,G,Dk,Dv,size", [(8, 2, 128, 128, 1200), (4, 4, 64, 32, 600), (6, 2, 64, 64, 0), (6, 6, 48, 48, 700),
+                                            (2, 1, 112, 112, 0)])
 def test_single_tokens_with_many_keys_join_their_runs_with_the_sink_counted_once(H, G, Dk, Dv, size):
     """Tokens deep in a sequence of 1,300 beside tokens near its start, in one call: the long ones' keys are cut into
     runs for several blocks and joined; the sink enters the joined denominator once, the gate the joined output."""

@@ -3,7 +3,8 @@
 //
 //   score(i, j) = q_i . k_j * scale - slope_h * (i - j),   slope_h = 2^(-bias_exp * (h + 1) / H)
 //   query i sees key j  iff  j <= i and (window == 0 or i - j < window or j < keep_first)
-//   keys of size DK (64, 128), values of size DV (32, 64, 128), which need not be equal
+//   keys of size DK (64, 128), values of size DV (32, 64, 128), which need not be equal; also equal sizes of
+//   32, 48, 80, 96 and 112 (a row of a size that is no power of two lies in shared memory padded to the next one)
 //   optionally a sink per query head: the softmax's denominator also holds exp(sinks[h]) (no key, no value,
 //   not scaled), and an output gate: head h's output times sigmoid(g), g the element at column
 //   gate_col + h of the token's row of `q`
@@ -31,6 +32,9 @@
 #define AB_BM 64
 #define AB_BN 64
 #define AB_LOG2E 1.4426950408889634f
+
+// The least power of two that is not below n (n >= 4 here: heads of at least 32 elements).
+__host__ __device__ constexpr int ab_pow2(int n) { return n <= 4 ? 4 : (n <= 8 ? 8 : 16); }
 
 template <int CH> __device__ __forceinline__ int ab_swz(int r, int cc) {
     // 16-byte chunk cc of row r; rows of 8 or 16 chunks XOR the row's low bits, rows of 4 chunks
@@ -69,7 +73,11 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                         const float* __restrict__ sinks, int gate_col) {
     extern __shared__ __align__(128) unsigned char ab_smem[];
     constexpr int KCH = DK / 8, VCH = DV / 8;
-    constexpr int K_BYTES = AB_BN * DK * 2, V_BYTES = AB_BN * DV * 2;
+    constexpr int KCHP = ab_pow2(KCH), VCHP = ab_pow2(VCH);   // a row's place in shared memory: chunks up to a power of two
+    constexpr int KROW = KCHP * 16, VROW = VCHP * 16;
+    constexpr int K_BYTES = AB_BN * KROW, V_BYTES = AB_BN * VROW;
+    constexpr int DVT = (DV + 31) / 32 * 4;   // output tiles of 8 columns, in fours (those past DV / 8 are computed on whatever
+                                              // the row's padding holds and never stored)
     pdl_wait();
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -101,14 +109,14 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
     const int n_kept_tiles = min((kept + AB_BN - 1) / AB_BN, tile_lo);   // tiles with kept positions, before the window's
     const int n_tiles = n_kept_tiles + tile_hi - tile_lo;
 
-    unsigned char* q_s = ab_smem;                    // [64][DK]
-    unsigned char* kv_s = ab_smem + AB_BM * DK * 2;  // 2 stages x (K tile, V tile)
+    unsigned char* q_s = ab_smem;                    // [64][DK, padded]
+    unsigned char* kv_s = ab_smem + AB_BM * KROW;  // 2 stages x (K tile, V tile)
 
     for (int c = threadIdx.x; c < AB_BM * KCH; c += AB_WARPS * 32) {
         const int r = c / KCH, cc = c % KCH;
         const int tr = min(t0 + (r >> share_log2), n_new - 1);   // rows past the end repeat the last token
         const int hd = head0 + (r & (share - 1));
-        cp_async16(q_s + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4),
+        cp_async16(q_s + r * KROW + (ab_swz<KCHP>(r, cc) << 4),
                    q + (size_t)(row_base + tr) * q_row_stride + (size_t)hd * DK + cc * 8);
     }
     cp_async_commit();
@@ -126,7 +134,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
             if (key >= kept) key = i < n_kept_tiles ? kept - 1 : max(min(key, kv_hi - 1), kv_lo);
             key = min(key, kv_hi - 1);
             const int page = bt[key / S];
-            cp_async16(ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4),
+            cp_async16(ks + r * KROW + (ab_swz<KCHP>(r, cc) << 4),
                        k_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DK + cc * 8);
         }
         for (int c = threadIdx.x; c < AB_BN * VCH; c += AB_WARPS * 32) {
@@ -135,7 +143,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
             if (key >= kept) key = i < n_kept_tiles ? kept - 1 : max(min(key, kv_hi - 1), kv_lo);
             key = min(key, kv_hi - 1);
             const int page = bt[key / S];
-            cp_async16(vs + r * (DV * 2) + (ab_swz<VCH>(r, cc) << 4),
+            cp_async16(vs + r * VROW + (ab_swz<VCHP>(r, cc) << 4),
                        v_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DV + cc * 8);
         }
     };
@@ -151,13 +159,13 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk) {
             const int cc = 2 * kk + (mi >> 1);
-            ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], q_s + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4));
+            ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], q_s + r * KROW + (ab_swz<KCHP>(r, cc) << 4));
         }
     }
 
-    float o[DV / 8][4];
+    float o[DVT][4];
 #pragma unroll
-    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int i = 0; i < DVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const int r0 = warp * 16 + (lane >> 2);
     const int pos0 = off + t0 + (r0 >> share_log2), pos1 = off + t0 + ((r0 + 8) >> share_log2);
@@ -199,7 +207,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                     for (int kg = 0; kg < AB_BN / 16; ++kg) {
                         const int r = kg * 16 + rr;
                         unsigned b00, b01, b10, b11;
-                        ldmatrix_x4(b00, b01, b10, b11, ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4));
+                        ldmatrix_x4(b00, b01, b10, b11, ks + r * KROW + (ab_swz<KCHP>(r, cc) << 4));
                         mma_bf16(sc[kg][0], qf[kk], b00, b01);
                         mma_bf16(sc[kg][1], qf[kk], b10, b11);
                     }
@@ -213,7 +221,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                     for (int kk = 0; kk < DK / 16; ++kk) {
                         const int cc = 2 * kk + (mi & 1);
                         unsigned b00, b01, b10, b11;
-                        ldmatrix_x4(b00, b01, b10, b11, ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4));
+                        ldmatrix_x4(b00, b01, b10, b11, ks + r * KROW + (ab_swz<KCHP>(r, cc) << 4));
                         mma_bf16(sc[kg][0], qf[kk], b00, b01);
                         mma_bf16(sc[kg][1], qf[kk], b10, b11);
                     }
@@ -254,7 +262,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                 l[hrow] = l[hrow] * alpha + ps;
                 m[hrow] = m_new;
 #pragma unroll
-                for (int i2 = 0; i2 < DV / 8; ++i2) {
+                for (int i2 = 0; i2 < DVT; ++i2) {
                     o[i2][2 * hrow] *= alpha;
                     o[i2][2 * hrow + 1] *= alpha;
                 }
@@ -274,12 +282,12 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                 }
                 const int r = kg * 16 + ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
-                for (int nt = 0; nt < DV / 8; nt += 4) {   // (two loads, then four independent pairs of products)
+                for (int nt = 0; nt < DVT; nt += 4) {   // (two loads, then four independent pairs of products)
                     unsigned v[2][4];
 #pragma unroll
                     for (int u = 0; u < 2; ++u)
                         ldmatrix_x4_trans(v[u][0], v[u][1], v[u][2], v[u][3],
-                                          vs + r * (DV * 2) + (ab_swz<VCH>(r, nt + 2 * u + (mi >> 1)) << 4));
+                                          vs + r * VROW + (ab_swz<VCHP>(r, nt + 2 * u + (mi >> 1)) << 4));
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
                         mma_bf16(o[nt + 2 * u], hi, v[u][0], v[u][1]);
@@ -334,7 +342,9 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
                      int S, int share_log2, float* __restrict__ scratch, const float* __restrict__ sinks, int gate_col) {
     extern __shared__ __align__(128) unsigned char ad_smem[];
     constexpr int KCH = DK / 8, VCH = DV / 8;
-    constexpr int K_BYTES = 16 * DK * 2, V_BYTES = 16 * DV * 2;
+    constexpr int KCHP = ab_pow2(KCH), VCHP = ab_pow2(VCH);
+    constexpr int KROW = KCHP * 16, VROW = VCHP * 16;
+    constexpr int K_BYTES = 16 * KROW, V_BYTES = 16 * VROW;
     constexpr int WARP_BYTES = 2 * (K_BYTES + V_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.y;
@@ -342,8 +352,8 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
     const int hk = share > 1 ? blockIdx.x : blockIdx.x / (H / Hk);
     const int head0 = share > 1 ? hk * share : blockIdx.x;
     unsigned char* q_s = ad_smem;                                  // [16][DK]
-    unsigned char* mine = ad_smem + 16 * DK * 2 + warp * WARP_BYTES;
-    float* part = reinterpret_cast<float*>(ad_smem + 16 * DK * 2); // after the walk: [warp][16 rows][DV + 2]
+    unsigned char* mine = ad_smem + 16 * KROW + warp * WARP_BYTES;
+    float* part = reinterpret_cast<float*>(ad_smem + 16 * KROW); // after the walk: [warp][16 rows][DV + 2]
     pdl_wait();
     pdl_trigger();
     const int pos = positions[t];
@@ -362,7 +372,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
     for (int c = threadIdx.x; c < 16 * KCH; c += AD_WARPS * 32) {
         const int r = c / KCH, cc = c % KCH;
         const int hd = head0 + min(r, share - 1);   // rows past the group repeat its last head
-        *reinterpret_cast<uint4*>(q_s + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4)) =
+        *reinterpret_cast<uint4*>(q_s + r * KROW + (ab_swz<KCHP>(r, cc) << 4)) =
             *reinterpret_cast<const uint4*>(q + (size_t)t * q_row_stride + (size_t)hd * DK + cc * 8);
     }
     auto issue = [&](int g, int stage) {
@@ -373,7 +383,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
             const int n = min(g * 16 + r, nkeys - 1);
             const int key = n < nkept ? n : start + n - nkept;
             const int page = bt[key / S];
-            cp_async16(ks + r * (DK * 2) + (ab_swz<KCH>(r, cc) << 4),
+            cp_async16(ks + r * KROW + (ab_swz<KCHP>(r, cc) << 4),
                        k_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DK + cc * 8);
         }
         for (int c = lane; c < 16 * VCH; c += 32) {
@@ -381,7 +391,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
             const int n = min(g * 16 + r, nkeys - 1);
             const int key = n < nkept ? n : start + n - nkept;
             const int page = bt[key / S];
-            cp_async16(vs + r * (DV * 2) + (ab_swz<VCH>(r, cc) << 4),
+            cp_async16(vs + r * VROW + (ab_swz<VCHP>(r, cc) << 4),
                        v_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DV + cc * 8);
         }
     };
@@ -394,7 +404,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
         const int r = ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
-            ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], q_s + r * (DK * 2) + (ab_swz<KCH>(r, 2 * kk + (mi >> 1)) << 4));
+            ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], q_s + r * KROW + (ab_swz<KCHP>(r, 2 * kk + (mi >> 1)) << 4));
     }
     float o[DV / 8][4];
 #pragma unroll
@@ -421,7 +431,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
 #pragma unroll
             for (int kk = 0; kk < DK / 16; ++kk) {
                 unsigned b00, b01, b10, b11;
-                ldmatrix_x4(b00, b01, b10, b11, ks + r * (DK * 2) + (ab_swz<KCH>(r, 2 * kk + (mi & 1)) << 4));
+                ldmatrix_x4(b00, b01, b10, b11, ks + r * KROW + (ab_swz<KCHP>(r, 2 * kk + (mi & 1)) << 4));
                 mma_bf16(sc[0], qf[kk], b00, b01);
                 mma_bf16(sc[1], qf[kk], b10, b11);
             }
@@ -473,7 +483,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
 #pragma unroll
         for (int nt = 0; nt < DV / 8; nt += 2) {
             unsigned v00, v01, v10, v11;
-            ldmatrix_x4_trans(v00, v01, v10, v11, vs + rv * (DV * 2) + (ab_swz<VCH>(rv, nt + (mi >> 1)) << 4));
+            ldmatrix_x4_trans(v00, v01, v10, v11, vs + rv * VROW + (ab_swz<VCHP>(rv, nt + (mi >> 1)) << 4));
             mma_bf16(o[nt], hi, v00, v01);
             mma_bf16(o[nt + 1], hi, v10, v11);
             mma_bf16(o[nt], lw, v00, v01);
@@ -554,8 +564,9 @@ static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_p
                                 bf16* out, int out_row_stride, float scale, float bias_exp, int window, int keep_first,
                                 int tokens, int H, int Hk, int S, float* scratch, int runs, const float* sinks, int gate_col,
                                 cudaStream_t stream) {
-    const size_t walk = (size_t)AD_WARPS * 2 * (16 * DK * 2 + 16 * DV * 2), parts = (size_t)AD_WARPS * 16 * (DV + 2) * 4;
-    const size_t smem = 16 * DK * 2 + (walk > parts ? walk : parts);
+    constexpr int KROW = ab_pow2(DK / 8) * 16, VROW = ab_pow2(DV / 8) * 16;
+    const size_t walk = (size_t)AD_WARPS * 2 * (16 * KROW + 16 * VROW), parts = (size_t)AD_WARPS * 16 * (DV + 2) * 4;
+    const size_t smem = 16 * KROW + (walk > parts ? walk : parts);
     static bool configured[VX_MAX_DEVICES];
     if (int rc = vx_configure_smem(biased_decode_kernel<DK, DV>, smem, configured)) return rc;
     const int G = H / Hk;
@@ -579,7 +590,8 @@ static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, co
                          int max_blocks, AbSegments seg, bf16* out, int out_row_stride, float scale, float bias_exp,
                          int window, int keep_first, int segments, int max_new, int H, int Hk, int S, const float* sinks,
                          int gate_col, cudaStream_t stream) {
-    const size_t smem = (size_t)AB_BM * DK * 2 + 2 * ((size_t)AB_BN * DK * 2 + (size_t)AB_BN * DV * 2);
+    constexpr int KROW = ab_pow2(DK / 8) * 16, VROW = ab_pow2(DV / 8) * 16;
+    const size_t smem = (size_t)AB_BM * KROW + 2 * ((size_t)AB_BN * KROW + (size_t)AB_BN * VROW);
     static bool configured[VX_MAX_DEVICES];
     if (int rc = vx_configure_smem(biased_attention_kernel<DK, DV>, smem, configured)) return rc;
     const int G = H / Hk;
@@ -618,6 +630,7 @@ extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* 
                                             scale, bias_exp, window, keep_first, segments, H, Hk, S, scratch, runs, sinks,  \
                                             gate_col, stream)
         AD_GO(64, 32); AD_GO(64, 64); AD_GO(64, 128); AD_GO(128, 32); AD_GO(128, 64); AD_GO(128, 128);
+        AD_GO(32, 32); AD_GO(48, 48); AD_GO(80, 80); AD_GO(96, 96); AD_GO(112, 112);
 #undef AD_GO
         return VX_ERR_SHAPE;
     }
@@ -628,6 +641,7 @@ extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* 
                                      max_blocks, seg, (bf16*)out, out_row_stride, scale, bias_exp, window, keep_first,    \
                                      segments, max_new, H, Hk, S, sinks, gate_col, stream)
     AB_GO(64, 32); AB_GO(64, 64); AB_GO(64, 128); AB_GO(128, 32); AB_GO(128, 64); AB_GO(128, 128);
+    AB_GO(32, 32); AB_GO(48, 48); AB_GO(80, 80); AB_GO(96, 96); AB_GO(112, 112);
 #undef AB_GO
     return VX_ERR_SHAPE;
 }

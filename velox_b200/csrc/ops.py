@@ -315,10 +315,16 @@ def _check_sinks_gate(what: str, sinks, gate_col: int, num_heads: int, q_row_str
 BIASED_DECODE_MAX_RUNS = 8
 
 
+BIASED_ATTENTION_EQUAL_SIZES = (32, 48, 80, 96, 112)
+
+
 def biased_attention_supported(dtype, head_dim: int, v_head_dim: int, page_size: int) -> bool:
-    """What the tensor-core kernel for attention with a bias by distance, a window with kept first positions
-    and values of another size than keys takes."""
-    return dtype == torch.bfloat16 and head_dim in (64, 128) and v_head_dim in (32, 64, 128) and page_size % 16 == 0
+    """What the tensor-core kernels for attention with a bias by distance, a window with kept first positions,
+    values of another size than keys, a sink and an output gate take: keys of 64 or 128 with values of 32, 64 or
+    128, or keys and values of one size out of 32, 48, 80, 96, 112."""
+    sizes = (head_dim in (64, 128) and v_head_dim in (32, 64, 128)) or \
+        (head_dim == v_head_dim and head_dim in BIASED_ATTENTION_EQUAL_SIZES)
+    return dtype == torch.bfloat16 and sizes and page_size % 16 == 0
 
 
 def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions,
