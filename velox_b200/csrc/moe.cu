@@ -36,6 +36,111 @@ __device__ __forceinline__ void route_load8(const bf16* p, float (&v)[8]) {
     for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
 }
 
+// Four consecutive elements of a token's row as they are loaded (one register pair or quad), and as floats.
+template <typename T> struct RouteRow;
+template <> struct RouteRow<float> {
+    typedef float4 packed;
+    static __device__ __forceinline__ void unpack(const float4& a, float (&v)[4]) { v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; }
+};
+template <> struct RouteRow<bf16> {
+    typedef uint2 packed;
+    static __device__ __forceinline__ void unpack(const uint2& r, float (&v)[4]) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+        const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+        v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+    }
+};
+
+// What follows a token's logits z[0 .. E) (and z[E], the shared gate's, if there is one), by the token's warp: the
+// shared gate, the scores, the choice and the weights, the experts' counters.  z, sc, gs (floats) and kept hold
+// MOE_MAX_EXPERTS (+ 8) entries of this warp's own, zc and pick MOE_MAX_TOP.
+__device__ __forceinline__ void route_select(float* z, float* sc, float* gs, unsigned char* kept, float* zc, int* pick, int lane, int t,
+                                             int E, int top, int* __restrict__ chosen, float* __restrict__ weight,
+                                             int* __restrict__ counts, int* __restrict__ pos, int mode,
+                                             const float* __restrict__ correction, int groups, int keep_groups,
+                                             float route_scale, float* __restrict__ shared_gate) {
+    if (shared_gate && lane == 0) shared_gate[t] = 1.f / (1.f + expf(-z[E]));
+    if (mode == 1) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - mx); sc[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) {
+            const float v = sc[e] / sum;
+            sc[e] = v;
+            z[e] = v + (correction ? correction[e] : 0.f);   // the choice score; the weight stays v
+        }
+        __syncwarp();
+        if (groups > 1 && keep_groups < groups) {
+            const int gsize = E / groups;
+            for (int g = lane; g < groups; g += 32) {
+                float b = -INFINITY;
+                for (int e = g * gsize; e < (g + 1) * gsize; ++e) b = fmaxf(b, z[e]);
+                gs[g] = b;
+                kept[g] = 0;
+            }
+            __syncwarp();
+            for (int i = 0; i < keep_groups; ++i) {
+                float best = -INFINITY;
+                int arg = 0x7fffffff;
+                for (int g = lane; g < groups; g += 32) {
+                    const float v = gs[g];
+                    if (!kept[g] && (v > best || (v == best && g < arg))) { best = v; arg = g; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                    if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+                }
+                if (lane == 0 && arg != 0x7fffffff) kept[arg] = 1;
+                __syncwarp();
+            }
+            for (int e = lane; e < E; e += 32)
+                if (!kept[e / gsize]) z[e] = -INFINITY;   // (not 0: a choice score may be negative)
+            __syncwarp();
+        }
+    }
+    for (int i = 0; i < top; ++i) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < arg)) { best = v; arg = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (lane == 0) {
+            zc[i] = mode == 1 ? sc[arg] : best;
+            z[arg] = -INFINITY;
+            pick[i] = arg;
+        }
+        __syncwarp();
+    }
+    // a lane a choice: the experts' counters are asked all at once (one after the other each costs a trip to the L2)
+    if (lane < top) {
+        const int e = pick[lane];
+        chosen[(size_t)t * top + lane] = e;
+        float w;
+        if (mode == 1) {
+            w = zc[lane] * route_scale;
+        } else {
+            const float m = zc[0];
+            float sum = 0.f;
+            for (int i = 0; i < top; ++i) sum += expf(zc[i] - m);
+            w = expf(zc[lane] - m) / sum;
+        }
+        weight[(size_t)t * top + lane] = w;
+        pos[(size_t)t * top + lane] = atomicAdd(&counts[e], 1);
+    }
+}
+
 #define ROUTE_KC 512
 // `vec`: K a multiple of 8 and 16-byte aligned rows (the host checks); else element by element.
 template <typename T>
@@ -46,6 +151,7 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
                  int groups, int keep_groups, float route_scale, float* __restrict__ shared_gate) {
     __shared__ float z_s[4][MOE_MAX_EXPERTS + 8];
     __shared__ float zc_s[4][MOE_MAX_TOP];
+    __shared__ int pick_s[4][MOE_MAX_TOP];
     __shared__ float sc_s[4][MOE_MAX_EXPERTS];      // mode 1: the scores of all outputs
     __shared__ float gs_s[4][MOE_MAX_EXPERTS];      //         the groups' scores
     __shared__ unsigned char kept_s[4][MOE_MAX_EXPERTS];
@@ -115,81 +221,88 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_r
     }
     if (!valid) return;
     __syncwarp();
-    if (shared_gate && lane == 0) shared_gate[t] = 1.f / (1.f + expf(-z[E]));
-    float* sc = sc_s[warp];
-    if (mode == 1) {
-        float mx = -INFINITY;
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
-        mx = warp_max(mx);
-        float sum = 0.f;
-        for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - mx); sc[e] = p; sum += p; }
-        sum = warp_sum(sum);
-        for (int e = lane; e < E; e += 32) {
-            const float v = sc[e] / sum;
-            sc[e] = v;
-            z[e] = v + (correction ? correction[e] : 0.f);   // the choice score; the weight stays v
+    route_select(z, sc_s[warp], gs_s[warp], kept_s[warp], zc_s[warp], pick_s[warp], lane, t, E, top, chosen, weight, counts, pos, mode,
+                 correction, groups, keep_groups, route_scale, shared_gate);
+}
+
+// The same with the router's whole matrix resident in shared memory: a block brings it in once (before it waits for
+// the step's earlier kernels: weights depend on none) and then walks its share of the tokens, 16 at a time, a warp a
+// token.  A lane takes 4 consecutive k of every 128, so that a warp's reads of a row are one run of 512 bytes.  The
+// warps' own arrays follow the matrix in the same dynamic shared memory, sized by the number of outputs.
+#define ROUTE_R_WARPS 16
+#define ROUTE_RESIDENT_MAX (220 * 1024)
+// a warp's own arrays: four of `entries` floats (logits, scores, group scores, flags), the chosen scores and outputs
+__host__ __device__ constexpr int route_warp_entries(int rows) { return ((rows + 7) & ~7) + 8; }
+__host__ __device__ constexpr int route_warp_floats(int rows) { return 4 * route_warp_entries(rows) + 2 * MOE_MAX_TOP; }
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_R_WARPS * 32)
+moe_route_resident_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w_router, const float* __restrict__ bias,
+                          int tokens, int K, int E, int top, int* __restrict__ chosen, float* __restrict__ weight,
+                          int* __restrict__ counts, int* __restrict__ pos, int mode, const float* __restrict__ correction,
+                          int groups, int keep_groups, float route_scale, float* __restrict__ shared_gate) {
+    extern __shared__ __align__(16) float rw_s[];   // [rows][K], then per warp: z, scores, group scores, kept flags, chosen
+    const int rows = E + (shared_gate ? 1 : 0);
+    const int ep = route_warp_entries(rows);
+    float* mine = rw_s + (size_t)rows * K + (size_t)(threadIdx.x >> 5) * route_warp_floats(rows);
+    {
+        const float4* src = reinterpret_cast<const float4*>(w_router);
+        float4* dst = reinterpret_cast<float4*>(rw_s);
+        const int n4 = rows * (K >> 2);
+        int i = threadIdx.x;
+        for (; i + 7 * ROUTE_R_WARPS * 32 < n4; i += 8 * ROUTE_R_WARPS * 32) {   // eight loads in flight a thread
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = src[i + u * ROUTE_R_WARPS * 32];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) dst[i + u * ROUTE_R_WARPS * 32] = v[u];
+        }
+        for (; i < n4; i += ROUTE_R_WARPS * 32) dst[i] = src[i];
+    }
+    pdl_wait();
+    pdl_trigger();
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* z = mine;
+    for (int t = blockIdx.x * ROUTE_R_WARPS + warp; t < tokens; t += gridDim.x * ROUTE_R_WARPS) {
+        const T* row = h + (size_t)t * ldh;
+        for (int e0 = 0; e0 < rows; e0 += 8) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            // the token's row comes 2,048 (bfloat16) or 1,024 (float) k at a time, every load of such a piece asked for
+            // before the first is used: one trip to memory a piece, not one every 128 k
+            constexpr int PIECE = sizeof(T) == 2 ? 16 : 8;
+            for (int k0 = lane * 4; k0 < K; k0 += PIECE * 128) {
+                typename RouteRow<T>::packed hp[PIECE];
+#pragma unroll
+                for (int c = 0; c < PIECE; ++c)
+                    if (k0 + c * 128 < K) hp[c] = *reinterpret_cast<const typename RouteRow<T>::packed*>(row + k0 + c * 128);
+#pragma unroll
+                for (int c = 0; c < PIECE; ++c) {
+                    const int k = k0 + c * 128;
+                    if (k < K) {
+                        float hv[4];
+                        RouteRow<T>::unpack(hp[c], hv);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 a = *reinterpret_cast<const float4*>(rw_s + (size_t)min(e0 + j, rows - 1) * K + k);
+                            acc[j] = fmaf(hv[0], a.x, acc[j]); acc[j] = fmaf(hv[1], a.y, acc[j]);
+                            acc[j] = fmaf(hv[2], a.z, acc[j]); acc[j] = fmaf(hv[3], a.w, acc[j]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float s = warp_sum(acc[j]);
+                if (lane == 0 && e0 + j < rows) z[e0 + j] = s + ((bias && e0 + j < E) ? bias[e0 + j] : 0.f);
+            }
         }
         __syncwarp();
-        if (groups > 1 && keep_groups < groups) {
-            const int gsize = E / groups;
-            float* gs = gs_s[warp];
-            unsigned char* kept = kept_s[warp];
-            for (int g = lane; g < groups; g += 32) {
-                float b = -INFINITY;
-                for (int e = g * gsize; e < (g + 1) * gsize; ++e) b = fmaxf(b, z[e]);
-                gs[g] = b;
-                kept[g] = 0;
-            }
-            __syncwarp();
-            for (int i = 0; i < keep_groups; ++i) {
-                float best = -INFINITY;
-                int arg = 0x7fffffff;
-                for (int g = lane; g < groups; g += 32) {
-                    const float v = gs[g];
-                    if (!kept[g] && (v > best || (v == best && g < arg))) { best = v; arg = g; }
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                    const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-                    if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
-                }
-                if (lane == 0 && arg != 0x7fffffff) kept[arg] = 1;
-                __syncwarp();
-            }
-            for (int e = lane; e < E; e += 32)
-                if (!kept[e / gsize]) z[e] = -INFINITY;   // (not 0: a choice score may be negative)
-            __syncwarp();
-        }
-    }
-    for (int i = 0; i < top; ++i) {
-        float best = -INFINITY;
-        int arg = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = z[e];
-            if (v > best || (v == best && e < arg)) { best = v; arg = e; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
-        }
-        if (lane == 0) {
-            zc_s[warp][i] = mode == 1 ? sc[arg] : best;
-            z[arg] = -INFINITY;
-            chosen[(size_t)t * top + i] = arg;
-            pos[(size_t)t * top + i] = atomicAdd(&counts[arg], 1);
-        }
+        route_select(z, mine + ep, mine + 2 * ep, reinterpret_cast<unsigned char*>(mine + 3 * ep), mine + 4 * ep,
+                     reinterpret_cast<int*>(mine + 4 * ep + MOE_MAX_TOP), lane, t, E, top,
+                     chosen, weight, counts, pos, mode, correction, groups, keep_groups, route_scale, shared_gate);
         __syncwarp();
-    }
-    if (lane == 0 && mode == 1) {
-        for (int i = 0; i < top; ++i) weight[(size_t)t * top + i] = zc_s[warp][i] * route_scale;
-    } else if (lane == 0) {
-        const float m = zc_s[warp][0];
-        float sum = 0.f;
-        for (int i = 0; i < top; ++i) sum += expf(zc_s[warp][i] - m);
-        for (int i = 0; i < top; ++i) weight[(size_t)t * top + i] = expf(zc_s[warp][i] - m) / sum;
     }
 }
 
@@ -199,14 +312,17 @@ moe_plan_kernel(const int* __restrict__ chosen, const int* __restrict__ pos, int
                 int E, int tile_rows, int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ n_tiles,
                 int* __restrict__ src_of_row, int* __restrict__ row_of, int tile_experts) {
     __shared__ int off_s[MOE_MAX_EXPERTS + 1];
+    __shared__ int cnt_s[MOE_MAX_EXPERTS];
     pdl_wait();
     pdl_trigger();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt_s[e] = counts[e];   // (together: the walk below would wait for each)
+    __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0, n = 0;
         for (int e = 0; e < E; ++e) {
             off_s[e] = run;
             offsets[e] = run;
-            const int c = counts[e];
+            const int c = cnt_s[e];
             // (outputs from `tile_experts` on are identity experts: their rows keep a place, no product walks them)
             for (int r = 0; r < c && e < tile_experts; r += tile_rows) {
                 tiles[3 * n] = e;
@@ -221,10 +337,23 @@ moe_plan_kernel(const int* __restrict__ chosen, const int* __restrict__ pos, int
         n_tiles[0] = n;
     }
     __syncthreads();
-    for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
-        const int p = off_s[chosen[a]] + pos[a];
-        src_of_row[p] = a;
-        row_of[a] = p;
+    for (int a0 = threadIdx.x; a0 < assignments; a0 += 4 * blockDim.x) {   // (four assignments' loads in flight a thread)
+        int c[4], q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int a = a0 + u * blockDim.x;
+            c[u] = a < assignments ? chosen[a] : 0;
+            q[u] = a < assignments ? pos[a] : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int a = a0 + u * blockDim.x;
+            if (a < assignments) {
+                const int p = off_s[c[u]] + q[u];
+                src_of_row[p] = a;
+                row_of[a] = p;
+            }
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;   // ready for the next step
@@ -247,6 +376,26 @@ extern "C" int vx_moe_route(const void* h, int ldh, const float* w_router, const
     const int blocks = (tokens + 3) / 4;
     const int elt = dtype == VX_F32 ? 4 : 2;
     const int vec = K % 8 == 0 && (ldh * elt) % 16 == 0 && !(((uintptr_t)h) & 15) && !(((uintptr_t)w_router) & 15);
+    // the router's matrix resident in shared memory where it fits (with the warps' own arrays behind it)
+    const int mrows = E + (shared_gate ? 1 : 0);
+    const size_t resident = ((size_t)mrows * K + (size_t)ROUTE_R_WARPS * route_warp_floats(mrows)) * sizeof(float);
+    if (vec && resident <= ROUTE_RESIDENT_MAX && (dtype == VX_F32 || dtype == VX_BF16)) {
+        static bool conf_f[VX_MAX_DEVICES], conf_b[VX_MAX_DEVICES];
+        static int sms[VX_MAX_DEVICES];
+        if (int rc = dtype == VX_F32 ? vx_configure_smem(moe_route_resident_kernel<float>, ROUTE_RESIDENT_MAX, conf_f)
+                                     : vx_configure_smem(moe_route_resident_kernel<bf16>, ROUTE_RESIDENT_MAX, conf_b)) return rc;
+        const int per_sm = 1;   // (512 threads with the token's row in registers: one block an SM)
+        int rblocks = (tokens + ROUTE_R_WARPS - 1) / ROUTE_R_WARPS;
+        if (rblocks > vx_sm_count(sms) * per_sm) rblocks = vx_sm_count(sms) * per_sm;
+        if (dtype == VX_F32)
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_route_resident_kernel<float>), rblocks, ROUTE_R_WARPS * 32, resident, stream,
+                        (const float*)h, ldh, w_router, bias, tokens, K, E, top, chosen, weight, counts, pos, mode, correction,
+                        groups, keep_groups, route_scale, shared_gate);
+        else
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_route_resident_kernel<bf16>), rblocks, ROUTE_R_WARPS * 32, resident, stream,
+                        (const bf16*)h, ldh, w_router, bias, tokens, K, E, top, chosen, weight, counts, pos, mode, correction,
+                        groups, keep_groups, route_scale, shared_gate);
+    } else
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (moe_route_kernel<float>), blocks, 128, 0, stream, (const float*)h, ldh, w_router, bias,
                     tokens, K, E, top, chosen, weight, counts, pos, vec, mode, correction, groups, keep_groups, route_scale,
