@@ -86,7 +86,16 @@ ALL = config(160, 128, [
     layer(_ALL0["mixer"], _ALL0["mlp"], weights_of=0),
 ], embedding_scale=1.5, logit_scale=0.5)
 
-CONFIGS = {"odd": ODD, "even": EVEN, "all": ALL}
+# heads of 48, 96 and 32 elements (sizes that lie in shared memory padded to a power of two), a width that is a multiple of 8
+# and not of 16, routers that choose every output
+MID = config(120, 104, [
+    layer(mixer(6, 3, 48, 48, 0.15, 50), moe(24, 3, 4, identity=1, scale=1.25, shared=40)),
+    layer(mixer(2, 1, 96, 96, 0.1, 17), None),
+    layer(mixer(4, 4, 32, 32, 0.18), moe(16, 2, 2)),
+    layer(mixer(6, 3, 48, 48, 0.15, 50), moe(24, 3, 4, identity=1, scale=1.25, shared=40), weights_of=0),
+], embedding_scale=2.0, logit_scale=0.3)
+
+CONFIGS = {"odd": ODD, "even": EVEN, "all": ALL, "mid": MID}
 
 
 def tensor_shapes(cfg):
@@ -132,7 +141,7 @@ def lively_weights(cfg, seed):
         elif name.endswith("q.norm") or name.endswith("k.norm"):
             x = 1.0 + 0.2 * rng.normal(size=shape)        # plain weights
         elif len(shape) == 1:
-            x = 0.1 * rng.normal(size=shape)              # stored around zero: the multiplier is 1 + x
+            x = 0.1 * rng.normal(size=shape)              # an offset: the multiplier is 1 + x
         elif name == "embed":
             x = rng.normal(0.0, 1.0, shape)
         else:

@@ -6,7 +6,7 @@ with the product path: it takes config.json as a dict and weights as a dict of n
 
 Notation: T tokens, E model width, positions p = 0 .. T-1.
   rms(x)   = x / sqrt(mean(x^2) + eps)
-  norm(x)  = rms(x) * (1 + w)                      (the weight is stored around zero)
+  norm(x)  = rms(x) * (1 + w)                      (the file holds w, an offset from one)
   input:   x = embed[token] * c_in
   layer:   x += norm_1(mix(x)) ;  x += norm_2(ff(x))     (the sublayers read x itself; no feed-forward: one line)
   mixer:   q, k, v = W h per head; q, k <- rms(.) * w_q, w_k over the head (plain weights, shared by the heads);

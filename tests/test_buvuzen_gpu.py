@@ -94,7 +94,8 @@ def test_the_residual_stream_after_every_layer_run(models):
 # position through the keys; so long bfloat16 runs use the configuration whose routers have nothing to decide, and
 # the routed ones run on sequences that have no close call.
 @pytest.mark.parametrize("name,dtype,length", [("odd", "float32", 150), ("even", "float32", 150), ("all", "float32", 150),
-                                               ("odd", "bfloat16", 40), ("all", "bfloat16", 150), ("even", "bfloat16", 24)])
+                                               ("odd", "bfloat16", 40), ("all", "bfloat16", 150), ("even", "bfloat16", 24),
+                                               ("mid", "float32", 100), ("mid", "bfloat16", 150)])
 def test_whole_prompts_portions_and_decoding_agree_with_the_plain_implementation(models, name, dtype, length):
     cfg, w, folder = models[name]
     toks, oracle = decided_tokens(cfg, w, length, 1) if (name, dtype) in (("even", "bfloat16"), ("odd", "bfloat16")) else (tokens_of(cfg, length, 1), None)

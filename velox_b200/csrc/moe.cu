@@ -272,6 +272,7 @@ moe_route_resident_kernel(const T* __restrict__ h, int ldh, const float* __restr
             // the token's row comes 2,048 (bfloat16) or 1,024 (float) k at a time, every load of such a piece asked for
             // before the first is used: one trip to memory a piece, not one every 128 k
             constexpr int PIECE = sizeof(T) == 2 ? 16 : 8;
+            const int nr = min(8, rows - e0);
             for (int k0 = lane * 4; k0 < K; k0 += PIECE * 128) {
                 typename RouteRow<T>::packed hp[PIECE];
 #pragma unroll
@@ -285,9 +286,11 @@ moe_route_resident_kernel(const T* __restrict__ h, int ldh, const float* __restr
                         RouteRow<T>::unpack(hp[c], hv);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const float4 a = *reinterpret_cast<const float4*>(rw_s + (size_t)min(e0 + j, rows - 1) * K + k);
-                            acc[j] = fmaf(hv[0], a.x, acc[j]); acc[j] = fmaf(hv[1], a.y, acc[j]);
-                            acc[j] = fmaf(hv[2], a.z, acc[j]); acc[j] = fmaf(hv[3], a.w, acc[j]);
+                            if (j < nr) {   // (the last group of rows may be short: nothing is read or added for the rest)
+                                const float4 a = *reinterpret_cast<const float4*>(rw_s + (size_t)(e0 + j) * K + k);
+                                acc[j] = fmaf(hv[0], a.x, acc[j]); acc[j] = fmaf(hv[1], a.y, acc[j]);
+                                acc[j] = fmaf(hv[2], a.z, acc[j]); acc[j] = fmaf(hv[3], a.w, acc[j]);
+                            }
                         }
                     }
                 }

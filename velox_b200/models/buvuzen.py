@@ -1,7 +1,7 @@
 """Buvuzen as a plan of parts.
 
 Input: the token's row times a multiplier.  Every layer is a post-norm block (the sublayers read the stream itself;
-each sublayer's OUTPUT is normed, with a weight stored around zero, and added) around softmax attention and a routed
+each sublayer's OUTPUT is normed, its multiplier one plus the stored tensor, and added) around softmax attention and a routed
 feed-forward, or no feed-forward, layer by layer as config.json lists them.  The attention runs over a paged cache
 without rotation (positions do not enter the scores): grouped key/value heads, q and k normed per head with plain
 weights shared by the heads, values of a size of their own, a sliding window, a learned sink per head in the

@@ -2,7 +2,7 @@
 
 The reference calls its tensor library's rms_norm with `rms_norm_eps`
 (src/paged/qwen3.rs:923-928, 933, 936); the weight multiplies, with no offset.
-With `one_plus` the stored tensor lies around zero and the multiplier is 1 + tensor
+With `one_plus` the stored tensor is the multiplier's offset from one: the multiplier is 1 + tensor
 (formed once in float32 when the weights are bound).
 """
 from __future__ import annotations
