@@ -174,6 +174,40 @@ def test_a_window_gives_its_pages_back_as_it_passes(models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_request_beside_short_ones_in_a_pool_made_for_what_is_live(models, dtype):
+    """700 tokens in portions that end inside pages and windows, beside a request that decodes token by token, ends, and
+    whose pages a third one takes; the pool holds what is live at any time (each request rounded up to 64 tokens) and
+    no more, so the windows' pages that went back are used again."""
+    cfg, w, folder = models["even" if dtype == "float32" else "all"]
+    toks = {"a": tokens_of(cfg, 700, 71), "b": tokens_of(cfg, 40, 72), "c": tokens_of(cfg, 60, 73)}
+    oracle = {k: Oracle(cfg, w, t) for k, t in toks.items()}
+    judge = RoundingJudge.of(oracle.values(), "buvuzen long request %s" % dtype)
+    engine = engine_for(folder, dtype, 704 + 64)
+    at = {k: 0 for k in toks}
+
+    def take(k, n):
+        lo = at[k]
+        hi = min(lo + n, len(toks[k]))
+        at[k] = hi
+        return (k, toks[k][lo:hi], list(range(hi - lo)), lo)
+
+    plan = [[("a", 128), ("b", 21)], [("a", 29), ("b", 1)], [("a", 2), ("b", 1)], [("a", 300), ("b", 1)]]
+    plan += [[("a", 1), ("b", 1)] for _ in range(16)] + [[("end", "b")], [("a", 1), ("c", 33)], [("a", 224), ("c", 1)]]
+    plan += [[("c", 2)], [("c", 24)], [("end", "a")], [("end", "c")]]
+    for step in plan:
+        if step[0][0] == "end":
+            run(engine, [[step[0]]])
+            continue
+        entries = [take(k, n) for k, n in step]
+        got = run(engine, [[(k, t, want) for k, t, want, _ in entries]])[0]
+        compare(got, [(oracle[k], lo, lo + len(t)) for k, t, _, lo in entries], dtype, "step %s" % (step,), judge)
+    assert all(at[k] == len(toks[k]) for k in toks)
+    assert all(g.allocator.num_free == g.allocator.num_pages for g in engine.cache.groups)
+    if dtype != "float32":
+        judge.finish()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(models, dtype):
     """360 tokens one by one after a short prompt: the windows pass over decoded tokens only, pages go back and are
     taken again, the captured step is replayed."""

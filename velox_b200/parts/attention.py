@@ -19,7 +19,8 @@ heads * v_head_dim), `keep_first` (with a window, the first positions stay visib
 to every later query, at their true distances), and `distance_bias_exponent` b > 0
 (head h's scores lose 2^(-b (h+1) / heads) * (query position - key position) before
 the softmax; 0: no bias).  With any of them the step's keys and values are written by
-the plain store kernel and the attention runs in the kernels that know them
+the plain store kernel (by the q/k norm's kernel, if q and k are normed or rotated: it takes a
+value size of its own) and the attention runs in the kernels that know them
 (`csrc/attention_biased.cu` for bfloat16, the general kernel otherwise).  `names` renames the four matrices
 and `norm_names` the two q/k norm weights.
 
