@@ -495,6 +495,8 @@ def buvuzen_kernels(pk, sz):
     flk = 2.0 * sum(min(i + 1, win) + (min(keep, i + 1 - win) if i + 1 > win else 0) for i in range(T)) * 2 * D * H
     row("prompt attention, window + sink + gate (mma.sync, P in two halves)", us(lambda: ops.biased_prefill_attention(
         q, width, kp, vp, bt, cu, off, D ** -0.5, win, 0, 0.0, H, G, D, D, 1, T, T, sinks=sinks, gate_col=gate_col)), fl)
+    row("prompt attention, window + sink + gate (tcgen05, P in two halves)", us(lambda: ops.paged_prefill_attention_tc(
+        q, width, kp, vp, bt, cu, off, D ** -0.5, win, H, G, D, 1, T, T, max_kv=T, halves=True, sinks=sinks, gate_col=gate_col)), fl)
     row("prompt attention, Dobepel (biased window, kept first tokens)", us(lambda: ops.biased_prefill_attention(
         q, width, kp, vp, bt, cu, off, D ** -0.5, win, keep, 8.0, H, G, D, D, 1, T, T)), flk)
     row("prompt attention, Qwen3 (tcgen05)", us(lambda: ops.paged_prefill_attention_tc(

@@ -84,6 +84,7 @@ ALL = config(160, 128, [
     layer(EVEN["layers"][1]["mixer"], None),
     layer(_EVEN2["mixer"], moe(64, 2, 2)),
     layer(_ALL0["mixer"], _ALL0["mlp"], weights_of=0),
+    layer(mixer(2, 2, 128, 128, 0.09, 45), None),    # (heads of 128 with values of 128: portions of 32 tokens or more on tcgen05)
 ], embedding_scale=1.5, logit_scale=0.5)
 
 # heads of 48, 96 and 32 elements (sizes that lie in shared memory padded to a power of two), a width that is a multiple of 8

@@ -130,6 +130,11 @@ def attend(kernel, q, gates, kp, vp, table, rows, dtype, scale, size, sinks, H, 
         return ops.biased_decode_attention(*args, ints([0] * T), ints(rows), scale, size, 0, 0.0, H, G, Dk, Dv, T,
                                            max_kv=max(rows) + 1, **more)
     assert rows == list(range(rows[0], rows[0] + T))
+    if kernel == "portion_tc":   # (the tcgen05 kernel with the probabilities in two halves; key tiles in runs when there are many)
+        got = ops.paged_prefill_attention_tc(*args, ints([0, T]), ints([rows[0]]), scale, size, H, G, Dk, 1, T, T,
+                                             max_kv=rows[-1] + 1, halves=True, **more)
+        ops.check_device_errors()
+        return got
     return ops.biased_prefill_attention(*args, ints([0, T]), ints([rows[0]]), scale, size, 0, 0.0, H, G, Dk, Dv, 1, T, T, **more)
 
 
@@ -138,16 +143,19 @@ def gated_plain(q, k, v, gates, scale, size, sinks):
     return o.reshape(q.shape[0], -1)
 
 
-KERNELS = [("general", torch.float32), ("general", torch.bfloat16), ("single", torch.bfloat16), ("portion", torch.bfloat16)]
+KERNELS = [("general", torch.float32), ("general", torch.bfloat16), ("single", torch.bfloat16), ("portion", torch.bfloat16),
+           ("portion_tc", torch.bfloat16)]
 
 
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
 @pytest.mark.parametrize("H,G,Dk,Dv,size", [(4, 2, 64, 32, 40), (8, 1, 64, 128, 100), (2, 2, 128, 64, 16), (4, 4, 64, 64, 300),
                                             (6, 2, 128, 128, 33), (3, 3, 64, 64, 0), (4, 2, 24, 20, 9), (5, 1, 48, 56, 70),
                                             (6, 3, 48, 48, 50), (4, 1, 32, 32, 21), (2, 2, 80, 80, 64), (4, 2, 96, 96, 17),
-                                            (3, 1, 112, 112, 130)])
+                                            (3, 1, 112, 112, 130), (8, 2, 128, 128, 100), (5, 1, 128, 128, 0), (4, 4, 128, 128, 300)])
 def test_sink_and_gate_attention_against_the_plain_function(kernel, dtype, H, G, Dk, Dv, size):
     from velox_b200.csrc import ops
+    if kernel == "portion_tc" and not (Dk == Dv == 128):
+        pytest.skip("the tcgen05 kernel takes heads of 128")
     if kernel != "general" and not ops.biased_attention_supported(dtype, Dk, Dv, 16):
         pytest.skip("sizes the tensor-core kernels do not take")
     rng = np.random.default_rng(H * (size + 1))
@@ -162,10 +170,25 @@ def test_sink_and_gate_attention_against_the_plain_function(kernel, dtype, H, G,
             continue
         if kernel == "single" and len(rows) > 60:
             rows = rows[::7]
-        if kernel == "portion" and len(rows) == 1:
+        if kernel in ("portion", "portion_tc") and len(rows) == 1:
             continue
         got = attend(kernel, q, gates, kp, vp, table, rows, dtype, scale, size, sinks, H, G, Dk, Dv)
         close(got, want[rows], TOL[dtype])
+
+
+@pytest.mark.parametrize("H,G,size", [(8, 2, 1200), (4, 4, 600), (5, 1, 0)])
+def test_the_tcgen05_kernel_joins_runs_of_key_tiles_with_the_sink_counted_once(H, G, size):
+    """A portion of 50 tokens on top of 1,250 cached ones: its key tiles are cut into runs for several blocks and joined;
+    beside it the same queries as one long prompt from the start (no runs)."""
+    rng = np.random.default_rng(size + H)
+    T, S, scale, D = 1300, 16, 0.1, 128
+    q, k, v = bf(rng.normal(size=(T, H, D))), bf(rng.normal(size=(T, G, D))), bf(rng.normal(size=(T, G, D)))
+    gates, sinks = bf(rng.normal(size=(T, H)) * 2), bf(rng.normal(size=H) * 2 + 3)
+    want = gated_plain(q, k, v, gates, scale, size, sinks)
+    kp, vp, table = paged(k, v, S, 90, 7)
+    for rows in (list(range(1250, 1300)), list(range(0, 1300)), list(range(700, 1100))):
+        got = attend("portion_tc", q, gates, kp, vp, table, rows, torch.bfloat16, scale, size, sinks, H, G, D, D, blocks=128)
+        close(got, want[rows], TOL[torch.bfloat16])
 
 
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
@@ -174,6 +197,8 @@ def test_a_sink_above_every_score_empties_the_row_and_one_far_below_changes_noth
     softmax), head 2 has the sink of a row's first token only (position 0: half of the weight goes to the sink when it
     equals the only score), head 3 a moderate one."""
     H, G, Dk, Dv, S, T, size, scale = 4, 2, 64, 32, 16, 70, 24, 0.125
+    if kernel == "portion_tc":
+        Dk = Dv = 128
     rng = np.random.default_rng(8)
     q, k, v = bf(rng.normal(size=(T, H, Dk)) * 0.3), bf(rng.normal(size=(T, G, Dk)) * 0.3), bf(rng.normal(size=(T, G, Dv)))
     q[0, 2], k[0, 1] = 0.0, 0.0
@@ -183,7 +208,7 @@ def test_a_sink_above_every_score_empties_the_row_and_one_far_below_changes_noth
     kp, vp, table = paged(k, v, S, 8, 1)
     want = gated_plain(q, k, v, gates, scale, size, sinks)
     plain = B.sink_window_attention(q, k, v, scale, size, np.full(H, -np.inf)).reshape(T, H, Dv)
-    for rows in ([0, 1], list(range(20, 70))) if kernel == "portion" else ([0], [1], [23], [24], [69]):
+    for rows in ([0, 1], list(range(20, 70))) if kernel in ("portion", "portion_tc") else ([0], [1], [23], [24], [69]):
         got = attend(kernel, q, gates, kp, vp, table, rows, dtype, scale, size, sinks, H, G, Dk, Dv)
         close(got, want[rows], TOL[dtype])
         g = got.float().cpu().numpy().reshape(len(rows), H, Dv)
@@ -193,9 +218,11 @@ def test_a_sink_above_every_score_empties_the_row_and_one_far_below_changes_noth
             assert np.abs(g[0, 2] - 0.5 * v[0, 1]).max() <= TOL[dtype] * max(1.0, np.abs(v).max())
 
 
-@pytest.mark.parametrize("Dk,Dv", [(64, 32), (48, 48), (96, 96)])
+@pytest.mark.parametrize("Dk,Dv", [(64, 32), (48, 48), (96, 96), (128, 128)])
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
 def test_one_key_that_stands_out_is_seen_exactly_as_long_as_the_window_says(kernel, dtype, Dk, Dv):
+    if (kernel == "portion_tc") != (Dk == 128):
+        pytest.skip("heads of 128 on the tcgen05 kernel, the others on the rest")
     """One key is made to dominate (a large dot product with every query) and its value is marked.  A query sees the
     mark iff the key is inside its window: at the window's last position and not one further, far away under no window,
     at page borders, with the key in the request's first page, in a prompt's portion and for single tokens.  A closed
@@ -214,12 +241,12 @@ def test_one_key_that_stands_out_is_seen_exactly_as_long_as_the_window_says(kern
         seen = [p for p in range(T) if spike <= p and (size == 0 or p - spike < size)]
         far = size if size else T
         edge = sorted({spike, spike + far - 1, spike + far, spike + far + 1, T - 1, 255, 256} & set(range(spike, T)))
-        if kernel != "portion":
+        if kernel not in ("portion", "portion_tc"):
             cases = [[p] for p in edge]
         else:
             cases = [list(range(max(0, spike - 3), T)), list(range(max(0, spike + far - 2), min(T, spike + far + 2)))]
         for rows in cases:
-            if kernel == "portion" and len(rows) < 2:
+            if kernel in ("portion", "portion_tc") and len(rows) < 2:
                 continue
             got = attend(kernel, q, gates, kp, vp, table, rows, dtype, scale, size, sinks, H, G, Dk, Dv)
             got = got.float().cpu().numpy().reshape(len(rows), H, Dv)

@@ -199,6 +199,12 @@ struct PtBarriers {
     unsigned long long s_full[PT_QTILES], p_ready[PT_QTILES], pv_done[PT_QTILES];
 };
 
+// EXT: the probabilities go to the tensor core in TWO bfloat16 halves, P = P_hi + P_lo (16 bits of mantissa together:
+// 32-bit weights in effect; P_hi takes columns 0-63 of the tile's scores, P_lo columns 64-127, and O += P_hi V + P_lo V
+// costs half as many products again), a sink per query head joins the softmax's denominator (2^(sink * log2 e), no key
+// and no value), and head h's output is multiplied by sigmoid of the element at column gate_col + h of the token's
+// row of the projections (`qrows`).  Without EXT the three parameters are not looked at.
+template <bool EXT>
 __global__ void __launch_bounds__(PT_THREADS, 1)
 paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                   const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
@@ -207,7 +213,8 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                                   bf16* __restrict__ out, int out_row_stride,
                                   float scale_log2, int window, int H, int Hk, int S, int share,
                                   float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits, int sms,
-                                  int* __restrict__ error) {
+                                  int* __restrict__ error, const float* __restrict__ sinks, const bf16* __restrict__ qrows,
+                                  int q_row_stride, int gate_col) {
     extern __shared__ unsigned char pt_smem_raw[];
     __shared__ __align__(8) PtBarriers bars;
     __shared__ unsigned tmem_base_s;
@@ -443,6 +450,12 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                         for (int k = 0; k < PT_KEYS / 16; ++k)   // 16 keys a step: 8 columns of packed P, 2 KB of V
                             pt_mma_ts(tmem_base + (unsigned)(256 + q * 128), tmem_base + (unsigned)(q * 128 + k * 8),
                                       pt_desc_mnmajor(va + (unsigned)(k * 2048)), idesc_o, (n > 0 || k > 0) ? 1u : 0u);
+                        if (EXT) {
+#pragma unroll
+                            for (int k = 0; k < PT_KEYS / 16; ++k)   // the probabilities' low halves, 64 columns on
+                                pt_mma_ts(tmem_base + (unsigned)(256 + q * 128), tmem_base + (unsigned)(q * 128 + 64 + k * 8),
+                                          pt_desc_mnmajor(va + (unsigned)(k * 2048)), idesc_o, 1u);
+                        }
                         pt_commit(pt_smem_u32(&bars.pv_done[q]));
                     }
                     if (t + 1 >= tile_a[q] && t + 1 < tile_b[q]) {
@@ -553,6 +566,28 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                 float2 sum2[4];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) sum2[c] = make_float2(0.f, 0.f);
+                if (EXT) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {   // 32 keys at a time: 16 columns of high halves, 16 of low ones
+                        unsigned hi[16], lo[16];
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const int jj = c * 32 + j;
+                            const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[jj]), __uint_as_float(v[jj + 1])), sc2, nm2);
+                            float2 p;
+                            p.x = pt_ex2(x.x);
+                            p.y = pt_ex2(x.y);
+                            sum2[(j >> 1) & 3] = __fadd2_rn(sum2[(j >> 1) & 3], p);
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(p.x, p.y);
+                            const float2 back = __bfloat1622float2(h);
+                            const __nv_bfloat162 w = __floats2bfloat162_rn(p.x - back.x, p.y - back.y);
+                            hi[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
+                            lo[j >> 1] = *reinterpret_cast<const unsigned*>(&w);
+                        }
+                        pt_st16(s_addr + (unsigned)(c * 16), hi);
+                        pt_st16(s_addr + (unsigned)(64 + c * 16), lo);
+                    }
+                } else
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     unsigned pk[32];
@@ -591,6 +626,19 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                     *reinterpret_cast<uint4*>(vt + (c16 >> 3) * PT_HALF_BYTES + row * 128 + (c16 & 7) * 16) =
                         make_uint4(0, 0, 0, 0);
                 }
+                // Groups of 16 keys below the block's window repeat the window's first group (see the producers); where
+                // that group is also the request's last one, its never-written slots came along with it: those rows too.
+                const int g_lo = kv_lo_all & ~15;
+                const int below = min(g_lo - t * PT_KEYS, first);   // rows of this tile that lie in groups below the window's
+                if (below > 0 && g_lo + 16 > kv_total) {
+                    const int slot0 = kv_total - g_lo;              // the group's first never-written slot
+                    for (int idx = quarter * 32 + lane; idx < below * 16; idx += PT_ROWS) {
+                        const int row = idx >> 4, c16 = idx & 15;
+                        if ((row & 15) >= slot0)
+                            *reinterpret_cast<uint4*>(vt + (c16 >> 3) * PT_HALF_BYTES + row * 128 + (c16 & 7) * 16) =
+                                make_uint4(0, 0, 0, 0);
+                    }
+                }
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             }
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
@@ -606,8 +654,23 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             if (lane == 0) { failed = 1; atomicExch(error, 13); }
         } else if (my_tiles > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const float inv = 1.f / l;
             const bool is_live = tok < my_live;
+            float f = 1.f;
+            if (EXT && is_live && splits <= 1) {   // (a run of several leaves sink and gate to the join)
+                if (sinks) {
+                    const float sk = sinks[hk * share + hi_] * PT_LOG2E;
+                    if (sk > m_used) {
+                        f = exp2f(m_used - sk);   // (the reference moves to the sink)
+                        l = l * f + 1.f;
+                    } else {
+                        l += exp2f(sk - m_used);
+                    }
+                }
+                if (gate_col >= 0)
+                    f /= 1.f + __expf(-__bfloat162float(qrows[(size_t)(row_base + my_t0 + tok) * q_row_stride + gate_col +
+                                                              hk * share + hi_]));
+            }
+            const float inv = f / l;
             bf16* dst = out + (size_t)(row_base + my_t0 + tok) * out_row_stride + (size_t)(hk * share + hi_) * PT_D;
             const size_t p = ((size_t)(row_base + my_t0 + tok) * H + (hk * share + hi_)) * max_splits + split;
 #pragma unroll 1
@@ -654,7 +717,8 @@ __global__ void __launch_bounds__(128)
 paged_prefill_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int max_splits, int sms,
                           const int* __restrict__ cu_seqlens, const int* __restrict__ kv_offsets,
                           const int* __restrict__ seq_list, bf16* __restrict__ out, int out_row_stride, int H, int Hk,
-                          int share) {
+                          int share, const float* __restrict__ sinks, const bf16* __restrict__ qrows, int q_row_stride,
+                          int gate_col) {
     pdl_wait();
     pdl_trigger();
     const int qt = blockIdx.x >> 5, hk = blockIdx.y;
@@ -686,7 +750,18 @@ paged_prefill_join_kernel(const float* __restrict__ part_o, const float* __restr
             const float4 v = *reinterpret_cast<const float4*>(part_o + (p0 + s2) * PT_D + lane * 4);
             o.x += wgt * v.x; o.y += wgt * v.y; o.z += wgt * v.z; o.w += wgt * v.w;
         }
-        const float inv = 1.f / L;
+        float f = 1.f;
+        if (sinks) {   // the sink joins the denominator once, where the runs are joined
+            const float sk = sinks[h] * PT_LOG2E;
+            if (sk > M) {
+                f = exp2f(M - sk);
+                L = L * f + 1.f;
+            } else {
+                L += exp2f(sk - M);
+            }
+        }
+        if (gate_col >= 0) f /= 1.f + __expf(-__bfloat162float(qrows[(size_t)row * q_row_stride + gate_col + h]));
+        const float inv = f / L;
         __nv_bfloat162 a = __floats2bfloat162_rn(o.x * inv, o.y * inv), b = __floats2bfloat162_rn(o.z * inv, o.w * inv);
         uint2 pk;
         pk.x = *reinterpret_cast<const unsigned*>(&a);
@@ -733,12 +808,11 @@ static bool pt_make_map(CUtensorMap* map, const void* base, long long rows, int 
 // with few query tiles and many keys cut their key tiles into up to so many runs
 // (pt_splits_of decides per request); `scratch` then holds tokens * H * max_splits *
 // (D + 2) floats.
-extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, int tokens, const void* k_pool,
-                                             const void* v_pool, int pages, const int* block_table, int max_blocks,
-                                             const int* cu_seqlens, const int* kv_offsets, const int* seq_list, void* out,
-                                             int out_row_stride, float scale, int window, int requests, int max_new,
-                                             int H, int Hk, int D, int S, float* scratch, int max_splits, int* error,
-                                             cudaStream_t stream) {
+static int pt_launch(bool ext, const float* sinks, int gate_col, const void* q, int q_row_stride, int tokens,
+                     const void* k_pool, const void* v_pool, int pages, const int* block_table, int max_blocks,
+                     const int* cu_seqlens, const int* kv_offsets, const int* seq_list, void* out, int out_row_stride,
+                     float scale, int window, int requests, int max_new, int H, int Hk, int D, int S, float* scratch,
+                     int max_splits, int* error, cudaStream_t stream) {
     if (requests <= 0 || max_new <= 0 || tokens <= 0) return VX_OK;
     if (D != PT_D || H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || !error) return VX_ERR_SHAPE;
     const int G = H / Hk;
@@ -755,8 +829,11 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
         !pt_make_map(&mv, v_pool, (long long)pages * Hk * S, D, D, 16))
         return VX_ERR_DRIVER;
     const size_t smem = 6 * (size_t)PT_TILE_BYTES + 1024;
-    static bool configured[VX_MAX_DEVICES];
-    if (int rc = vx_configure_smem(paged_prefill_attention_tc_kernel, smem, configured)) return rc;
+    static bool configured[VX_MAX_DEVICES], configured_ext[VX_MAX_DEVICES];
+    if (int rc = ext ? vx_configure_smem(paged_prefill_attention_tc_kernel<true>, smem, configured_ext)
+                     : vx_configure_smem(paged_prefill_attention_tc_kernel<false>, smem, configured)) return rc;
+    if (ext && gate_col >= 0 && gate_col + H > q_row_stride) return VX_ERR_SHAPE;
+    if (!ext) { sinks = nullptr; gate_col = -1; }
     const int q_tiles = (max_new + toks_per_tile - 1) / toks_per_tile;
     static int sm_counts[VX_MAX_DEVICES];
     const int sms = vx_sm_count(sm_counts);
@@ -765,15 +842,46 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
     float* part_ml = scratch ? scratch + (size_t)tokens * H * max_splits * D : nullptr;
     const int q_blocks = (q_tiles + PT_QTILES - 1) / PT_QTILES;
     dim3 grid(q_blocks * Hk * max_splits, 1, requests);
-    VX_LAUNCH_K(VX_K_ATTENTION, paged_prefill_attention_tc_kernel, grid, PT_THREADS, smem, stream, mq, mk, mv,
-                block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, scale * PT_LOG2E, window, H,
-                Hk, S, G, part_o, part_ml, max_splits, sms, error);
+    if (ext)
+        VX_LAUNCH_K(VX_K_ATTENTION, paged_prefill_attention_tc_kernel<true>, grid, PT_THREADS, smem, stream, mq, mk, mv,
+                    block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, scale * PT_LOG2E,
+                    window, H, Hk, S, G, part_o, part_ml, max_splits, sms, error, sinks, (const bf16*)q, q_row_stride, gate_col);
+    else
+        VX_LAUNCH_K(VX_K_ATTENTION, paged_prefill_attention_tc_kernel<false>, grid, PT_THREADS, smem, stream, mq, mk, mv,
+                    block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, scale * PT_LOG2E,
+                    window, H, Hk, S, G, part_o, part_ml, max_splits, sms, error, sinks, (const bf16*)q, q_row_stride, gate_col);
     VX_LAUNCH_CHECK();
     if (max_splits > 1) {
         dim3 jgrid(q_tiles * 32, Hk, requests);
         VX_LAUNCH_K(VX_K_JOIN, paged_prefill_join_kernel, jgrid, 128, 0, stream, (const float*)part_o, (const float*)part_ml,
-                    max_splits, sms, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, H, Hk, G);
+                    max_splits, sms, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, H, Hk, G, sinks,
+                    (const bf16*)q, q_row_stride, gate_col);
         VX_LAUNCH_CHECK();
     }
     return VX_OK;
+}
+
+extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, int tokens, const void* k_pool,
+                                             const void* v_pool, int pages, const int* block_table, int max_blocks,
+                                             const int* cu_seqlens, const int* kv_offsets, const int* seq_list, void* out,
+                                             int out_row_stride, float scale, int window, int requests, int max_new,
+                                             int H, int Hk, int D, int S, float* scratch, int max_splits, int* error,
+                                             cudaStream_t stream) {
+    return pt_launch(false, nullptr, -1, q, q_row_stride, tokens, k_pool, v_pool, pages, block_table, max_blocks, cu_seqlens,
+                     kv_offsets, seq_list, out, out_row_stride, scale, window, requests, max_new, H, Hk, D, S, scratch,
+                     max_splits, error, stream);
+}
+
+// The same with the probabilities in two bfloat16 halves (32-bit softmax weights in effect), an optional sink per query
+// head (float32, in the scores' natural units) and an optional output gate (gate_col >= 0: head h's output times
+// sigmoid of column gate_col + h of the token's row of `q`).
+extern "C" int vx_paged_prefill_attention_tc_ext(const void* q, int q_row_stride, int tokens, const void* k_pool,
+                                                 const void* v_pool, int pages, const int* block_table, int max_blocks,
+                                                 const int* cu_seqlens, const int* kv_offsets, const int* seq_list, void* out,
+                                                 int out_row_stride, float scale, int window, int requests, int max_new,
+                                                 int H, int Hk, int D, int S, float* scratch, int max_splits, int* error,
+                                                 const float* sinks, int gate_col, cudaStream_t stream) {
+    return pt_launch(true, sinks, gate_col, q, q_row_stride, tokens, k_pool, v_pool, pages, block_table, max_blocks, cu_seqlens,
+                     kv_offsets, seq_list, out, out_row_stride, scale, window, requests, max_new, H, Hk, D, S, scratch,
+                     max_splits, error, stream);
 }

@@ -91,6 +91,7 @@ def _declare(lib) -> None:
         "vx_gemm_tcgen05_pair": [P, P, P, P, I, I, I, I, I, I, I, I, P, P],
         "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
         "vx_paged_prefill_attention_tc": [P, I, I, P, P, I, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P, I, P, P],
+        "vx_paged_prefill_attention_tc_ext": [P, I, I, P, P, I, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P, I, P, P, I, P],
         "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, I, P],
         "vx_sample": [P, I, I, I, P, P, P, P, P],
@@ -795,12 +796,17 @@ def prefill_attention_tc_supported(dtype, head_dim: int, page_size: int, group: 
 def paged_prefill_attention_tc(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
                                cu_seqlens, kv_offsets, scale: float, window: int, num_heads: int, num_kv_heads: int,
                                head_dim: int, requests: int, max_new: int, tokens: int, seq_list=None,
-                               out: Optional[torch.Tensor] = None, max_kv: int = 0) -> torch.Tensor:
+                               out: Optional[torch.Tensor] = None, max_kv: int = 0, halves: bool = False, sinks=None,
+                               gate_col: int = -1) -> torch.Tensor:
     """The same as `paged_prefill_attention` on the tcgen05 tensor cores (head size
     128, accumulators in tensor memory, operands by TMA).  `max_kv` (a bound on any
     request's keys after the step) lets short portions on top of many keys be cut into
-    runs of key tiles that several blocks share; 0: never."""
-    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_list, out)
+    runs of key tiles that several blocks share; 0: never.  `halves`: the probabilities go to the
+    tensor core as two bfloat16 halves (32-bit softmax weights in effect; half as many products again);
+    with it `sinks` and `gate_col` as in `paged_attention_generic`."""
+    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_list, out, sinks)
+    _need(halves or (sinks is None and gate_col < 0), "paged_prefill_attention_tc: a sink and a gate go with halves=True")
+    _check_sinks_gate("paged_prefill_attention_tc", sinks, gate_col, num_heads, q_row_stride)
     _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
           "paged_prefill_attention_tc: bfloat16 only")
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
@@ -816,11 +822,15 @@ def paged_prefill_attention_tc(q: torch.Tensor, q_row_stride: int, k_pool, v_poo
     if max_kv >= 8 * 128 and 2 * -(-max_new // (2 * toks_per_tile)) * num_kv_heads <= sms:   # (a block takes two query tiles)
         max_splits = max(1, min(PREFILL_MAX_SPLITS, -(-max_kv // 128) // 4, sms // num_kv_heads))
         scratch = workspace(q.device, tokens * num_heads * max_splits * (head_dim + 2), which="prefill")
-    _check(library().vx_paged_prefill_attention_tc(
-        _ptr(q), q_row_stride, tokens, _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
-        block_table.shape[1], _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(seq_list), _ptr(out), num_heads * head_dim, float(scale),
-        int(window), requests, int(max_new), num_heads, num_kv_heads, head_dim, k_pool.shape[2],
-        _ptr(scratch), max_splits, _ptr(_error_word(q.device)), _stream()), "paged_prefill_attention_tc")
+    args = (_ptr(q), q_row_stride, tokens, _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
+            block_table.shape[1], _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(seq_list), _ptr(out), num_heads * head_dim, float(scale),
+            int(window), requests, int(max_new), num_heads, num_kv_heads, head_dim, k_pool.shape[2],
+            _ptr(scratch), max_splits, _ptr(_error_word(q.device)))
+    if halves:
+        _check(library().vx_paged_prefill_attention_tc_ext(*args, _ptr(sinks), int(gate_col), _stream()),
+               "paged_prefill_attention_tc (halves)")
+    else:
+        _check(library().vx_paged_prefill_attention_tc(*args, _stream()), "paged_prefill_attention_tc")
     note_bounded_wait()
     return out
 

@@ -210,6 +210,14 @@ class PagedAttention(Mixer):
     def _attend_extended(self, qkv, ctx, cache, group) -> torch.Tensor:
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
         more = dict(sinks=self.sinks, gate_col=self.gate_col)
+        page = cache.k_pool.shape[2]
+        if (not ctx.decode_only and ctx.max_new >= TC_PREFILL_MIN_TOKENS and self.keep_first == 0 and self.bias_exponent == 0
+                and self.v_head_dim == D and ops.prefill_attention_tc_supported(qkv.dtype, D, page, H // Hk)):
+            # prompt portions of heads of 128 without a bias by distance: the tcgen05 kernel, with the probabilities in two
+            # bfloat16 halves (this path's softmax weights are 32-bit), the sink and the gate in its epilogue
+            return ops.paged_prefill_attention_tc(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table, ctx.cu_seqlens,
+                                                  ctx.kv_offsets, self.scale, self.window, H, Hk, D, ctx.n_seqs, ctx.max_new,
+                                                  qkv.shape[0], max_kv=ctx.max_kv, halves=True, **more)
         if ops.biased_attention_supported(qkv.dtype, D, self.v_head_dim, cache.k_pool.shape[2]):
             # a step of single tokens: every row with its own position, its keys dealt to the warps of a block
             if ctx.decode_only:
